@@ -1,0 +1,41 @@
+"""Dense gated feed-forward (kind "gated_mlp"): down(silu(gate(x)) * up(x)).
+
+The reference fuses gate and up into one [2I, H] matrix, gate half first
+(engine/model.py:116, engine/kernels/swiglu.py:5-6), and rounds gate, up,
+silu(gate) and the product to bfloat16 (engine/kernels/swiglu.py:21-24).
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .registry import register_part
+
+
+class GatedMLP:
+    @staticmethod
+    def weight_shapes(spec):
+        return {
+            "gate": (spec.intermediate_size, spec.hidden_size),
+            "up": (spec.intermediate_size, spec.hidden_size),
+            "down": (spec.hidden_size, spec.intermediate_size),
+        }
+
+    def __init__(self, spec, weights, runtime):
+        if spec.activation != "silu":
+            raise ValueError(f"activation {spec.activation!r} is not built; only 'silu' is")
+        self.hidden_size = spec.hidden_size
+        self.intermediate_size = spec.intermediate_size
+        self.ops = runtime.ops
+        self.w_gate_up = self.ops.prepare_matrix(torch.cat([weights["gate"], weights["up"]], dim=0))
+        self.w_down = self.ops.prepare_matrix(weights["down"])
+
+    def prepare(self, cache) -> None:
+        pass
+
+    def forward(self, ctx, h):
+        act = self.ops.linear_swiglu(h, self.w_gate_up)
+        return self.ops.linear(act, self.w_down)
+
+
+register_part("ff", "gated_mlp", GatedMLP)
