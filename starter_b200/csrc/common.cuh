@@ -1,0 +1,97 @@
+// Shared definitions of the sm_100a kernels: element types, the step's batch
+// description, the paged key/value view of one layer, and small helpers.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define SB_PAGE 64  // tokens per cache page; must match starter_b200.cache.cache.PAGE
+
+enum { SB_F32 = 0, SB_BF16 = 1 };
+enum { SB_STATUS_BAD_TOKEN = 1, SB_STATUS_NO_PAGE = 2 };
+
+// A step's ragged batch.  Row r belongs to sequence row_seq[r]; that sequence sits in
+// cache slot seq_slot[s], brought rows cu_q[s]..cu_q[s+1]-1, and held lengths[slot]
+// tokens before the step, so row r stands at position lengths[slot] + r - cu_q[s].
+struct SbBatch {
+    const int* seq_slot;
+    const int* cu_q;
+    const int* row_seq;
+    const int* lengths;
+    int n_seqs;
+    int n_rows;
+    int null_slot;
+    int reserved;
+};
+
+// One layer's keys and values: pages [page][kv_head][SB_PAGE][head_dim]; the page of
+// position p of a slot is table[slot][p / SB_PAGE], or table[slot][(p / SB_PAGE) % ring_pages]
+// for a window group that keeps a ring of pages.
+struct SbKV {
+    void* k;
+    void* v;
+    const int* table;
+    int table_width;
+    int ring_pages;
+    int n_kv_heads;
+    int head_dim;
+};
+
+template <class T> __device__ __forceinline__ float to_f(T v);
+template <> __device__ __forceinline__ float to_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <class T> __device__ __forceinline__ T from_f(float v);
+template <> __device__ __forceinline__ float from_f<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+// The value as it reads back after being stored in T.
+template <class T> __device__ __forceinline__ float rnd(float v) { return to_f<T>(from_f<T>(v)); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `red` holds 33 floats.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, n_warps = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    if (warp == 0) {
+        float t = lane < n_warps ? red[lane] : 0.f;
+        t = warp_sum(t);
+        if (lane == 0) red[32] = t;
+    }
+    __syncthreads();
+    return red[32];
+}
+
+__device__ __forceinline__ void row_place(const SbBatch& b, int row, int& slot, int& pos) {
+    const int s = b.row_seq[row];
+    slot = b.seq_slot[s];
+    pos = b.lengths[slot] + row - b.cu_q[s];
+}
+
+// Element offset of [page][kv_head][pos % SB_PAGE][0] for a slot's position, or -1 when the
+// slot has no page there.
+__device__ __forceinline__ long long kv_offset(const SbKV& kv, int slot, int pos, int kv_head) {
+    int lp = pos / SB_PAGE;
+    if (kv.ring_pages) lp %= kv.ring_pages;
+    if (lp >= kv.table_width) return -1;
+    const int page = kv.table[(long long)slot * kv.table_width + lp];
+    if (page < 0) return -1;
+    return (((long long)page * kv.n_kv_heads + kv_head) * SB_PAGE + (pos % SB_PAGE)) * kv.head_dim;
+}
+
+#define SB_LAUNCH_CHECK() return (int)cudaGetLastError()

@@ -1,0 +1,231 @@
+"""The call table of the CUDA extension: torch tensors in, kernels launched on torch's current stream.
+
+Every function here launches hand-written sm_100a kernels from this folder's
+``.cu`` files through their ``extern "C"`` entry points.  Matrix products in
+bfloat16 with many rows go to cuBLAS through ``torch.matmul``, where the
+reference's engine calls the same library (engine/model.py:291,295,297,299).
+There is no CPU path and no other backend: without a CUDA device or without
+the compiled library, ``get_ops`` raises.
+"""
+
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, c_float, c_int, c_ulonglong, c_void_p
+
+import torch
+
+from .build import BuildError, load
+
+F32, BF16 = 0, 1
+
+
+class KernelError(RuntimeError):
+    """A kernel launch was refused (sizes it does not take) or failed."""
+
+
+class SbBatch(Structure):
+    _fields_ = [("seq_slot", c_void_p), ("cu_q", c_void_p), ("row_seq", c_void_p), ("lengths", c_void_p),
+                ("n_seqs", c_int), ("n_rows", c_int), ("null_slot", c_int), ("reserved", c_int)]
+
+
+class SbKV(Structure):
+    _fields_ = [("k", c_void_p), ("v", c_void_p), ("table", c_void_p), ("table_width", c_int),
+                ("ring_pages", c_int), ("n_kv_heads", c_int), ("head_dim", c_int)]
+
+
+def _code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, not {dtype}")
+
+
+def _ptr(t):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+class Ops:
+    name = "cuda"
+
+    # bfloat16 products with at most this many rows stay on this library's own kernels
+    GENERAL_GEMM_MAX_WORK = 1 << 22
+
+    def __init__(self, lib: ctypes.CDLL):
+        self.lib = lib
+        lib.sb_error_string.restype = ctypes.c_char_p
+        lib.sb_error_string.argtypes = [c_int]
+        sig = {
+            "sb_embed": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
+            "sb_gather_rows": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+            "sb_rmsnorm": [c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p],
+            "sb_swiglu": [c_int, c_void_p, c_void_p, c_int, c_int, c_void_p],
+            "sb_advance_lengths": [SbBatch, c_void_p, c_void_p],
+            "sb_gemm_general": [c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+            "sb_qk_rope_store": [c_int, c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_int, c_void_p, c_void_p,
+                                 c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
+            "sb_attention_general": [c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_void_p],
+            "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+            "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
+                          c_void_p],
+        }
+        for name, argtypes in sig.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = c_int
+
+    # ---- plumbing -----------------------------------------------------------------------
+
+    @staticmethod
+    def _stream():
+        return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def _check(self, code: int, what: str) -> None:
+        if code:
+            raise KernelError(f"{what}: {self.lib.sb_error_string(code).decode()} (code {code})")
+
+    @staticmethod
+    def _batch(ctx) -> SbBatch:
+        b = ctx.scratch.get("sb_batch")
+        if b is None:
+            b = SbBatch(ctx.seq_slot.data_ptr(), ctx.cu_q.data_ptr(), ctx.row_seq.data_ptr(), ctx.lengths.data_ptr(),
+                        ctx.n_seqs, ctx.n_rows, ctx.cache.null_slot, 0)
+            ctx.scratch["sb_batch"] = b
+        return b
+
+    @staticmethod
+    def _kv(layer_cache) -> SbKV:
+        kv = getattr(layer_cache, "_sb_kv", None)
+        if kv is None:
+            g = layer_cache.group
+            kv = SbKV(layer_cache.k.data_ptr(), layer_cache.v.data_ptr(), g.table.data_ptr(), g.table_width,
+                      g.ring_pages, g.request.num_kv_heads, g.request.head_dim)
+            layer_cache._sb_kv = kv
+        return kv
+
+    def prepare_matrix(self, w: torch.Tensor) -> torch.Tensor:
+        """A weight matrix [out, in] as the products want it: contiguous, in the run's dtype."""
+        if w.dim() != 2:
+            raise KernelError(f"a weight matrix has two axes, got shape {tuple(w.shape)}")
+        _code(w.dtype)
+        return w.contiguous()
+
+    # ---- rows ---------------------------------------------------------------------------
+
+    def embed(self, tokens, table, status):
+        out = torch.empty((tokens.shape[0], table.shape[1]), dtype=table.dtype, device=table.device)
+        self._check(self.lib.sb_embed(_code(table.dtype), _ptr(tokens), _ptr(table), _ptr(out), tokens.shape[0],
+                                      table.shape[1], table.shape[0], _ptr(status), self._stream()), "embed")
+        return out
+
+    def gather_rows(self, x, rows):
+        out = torch.empty((rows.shape[0], x.shape[1]), dtype=x.dtype, device=x.device)
+        self._check(self.lib.sb_gather_rows(_code(x.dtype), _ptr(x), _ptr(rows), _ptr(out), rows.shape[0], x.shape[1],
+                                            self._stream()), "gather_rows")
+        return out
+
+    def _norm_dtypes(self, x, w):
+        if x.dtype == torch.float32 and w.dtype != torch.float32:
+            raise KernelError("a float32 run needs float32 norm weights")
+        return _code(x.dtype), _code(w.dtype)
+
+    def rmsnorm(self, x, w, eps):
+        dt, wdt = self._norm_dtypes(x, w)
+        out = torch.empty_like(x)
+        self._check(self.lib.sb_rmsnorm(dt, wdt, _ptr(x), None, _ptr(w), _ptr(out), x.shape[0], x.shape[1], eps,
+                                        self._stream()), "rmsnorm")
+        return out
+
+    def add_rmsnorm(self, x, delta, w, eps):
+        dt, wdt = self._norm_dtypes(x, w)
+        out = torch.empty_like(x)
+        self._check(self.lib.sb_rmsnorm(dt, wdt, _ptr(x), _ptr(delta), _ptr(w), _ptr(out), x.shape[0], x.shape[1], eps,
+                                        self._stream()), "add_rmsnorm")
+        return out
+
+    def swiglu(self, gu):
+        inter = gu.shape[1] // 2
+        out = torch.empty((gu.shape[0], inter), dtype=gu.dtype, device=gu.device)
+        self._check(self.lib.sb_swiglu(_code(gu.dtype), _ptr(gu), _ptr(out), gu.shape[0], inter, self._stream()), "swiglu")
+        return out
+
+    def advance_lengths(self, ctx):
+        self._check(self.lib.sb_advance_lengths(self._batch(ctx), _ptr(ctx.lengths), self._stream()), "advance_lengths")
+
+    # ---- products -----------------------------------------------------------------------
+
+    def linear(self, a, w, out_float32=False):
+        """a [M, K] times w [N, K] transposed -> [M, N] in a's dtype, or 32-bit when asked."""
+        M, K = a.shape
+        N = w.shape[0]
+        if w.shape[1] != K or a.dtype != w.dtype:
+            raise KernelError(f"linear: a is {tuple(a.shape)} {a.dtype}, w is {tuple(w.shape)} {w.dtype}")
+        if a.dtype == torch.bfloat16 and M * N * K > self.GENERAL_GEMM_MAX_WORK and K % 8 == 0:
+            if out_float32:
+                return torch.mm(a, w.t(), out_dtype=torch.float32)
+            return torch.mm(a, w.t())
+        out = torch.empty((M, N), dtype=torch.float32 if out_float32 else a.dtype, device=a.device)
+        self._check(self.lib.sb_gemm_general(_code(a.dtype), int(out_float32 or a.dtype == torch.float32), _ptr(a), _ptr(w),
+                                             _ptr(out), M, N, K, self._stream()), "gemm_general")
+        return out
+
+    def linear_swiglu(self, h, w_gate_up):
+        return self.swiglu(self.linear(h, w_gate_up))
+
+    # ---- attention ----------------------------------------------------------------------
+
+    def qk_norm_rope_store(self, ctx, qkv, layer_cache, n_heads, n_kv_heads, head_dim, q_norm, k_norm, eps, rotary):
+        dt = _code(qkv.dtype)
+        wdt = _code(q_norm.dtype) if q_norm is not None else dt
+        if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
+            raise KernelError("qk_norm_rope_store: qkv has the wrong width")
+        q = torch.empty((qkv.shape[0], n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        cos = sin = None
+        rotary_dim = 0
+        if rotary is not None:
+            cos, sin, rotary_dim = rotary
+            if cos.dtype != qkv.dtype or cos.shape[1] * 2 != rotary_dim:
+                raise KernelError("qk_norm_rope_store: rotary tables do not fit the run")
+            if cos.shape[0] < ctx.kv_bound:
+                raise KernelError(f"the rotary table covers {cos.shape[0]} positions, the step reaches {ctx.kv_bound}")
+        kv = self._kv(layer_cache)
+        if kv.head_dim != head_dim or (n_kv_heads and kv.n_kv_heads != n_kv_heads):
+            raise KernelError("qk_norm_rope_store: the layer's cache has other head sizes than the mixer")
+        self._check(self.lib.sb_qk_rope_store(dt, wdt, _ptr(qkv), _ptr(q), self._batch(ctx), kv, n_heads, n_kv_heads,
+                                              _ptr(q_norm), _ptr(k_norm), eps, _ptr(cos), _ptr(sin), rotary_dim,
+                                              _ptr(ctx.status), self._stream()), "qk_rope_store")
+        return q
+
+    def attention(self, ctx, q, layer_cache, n_heads, scale, window):
+        out = torch.empty_like(q)
+        self._check(self.lib.sb_attention_general(_code(q.dtype), _ptr(q), _ptr(out), self._batch(ctx), self._kv(layer_cache),
+                                                  n_heads, scale, int(window or 0), self._stream()), "attention_general")
+        return out
+
+    # ---- sampling -----------------------------------------------------------------------
+
+    def argmax(self, logits):
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        self._check(self.lib.sb_argmax(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], self._stream()), "argmax")
+        return out
+
+    def sample(self, logits, temperature, top_k, seed, request_ids, steps, advance=False):
+        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        self._check(self.lib.sb_sample(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], float(temperature),
+                                       int(top_k), int(seed) & ((1 << 64) - 1), _ptr(request_ids), _ptr(steps),
+                                       int(bool(advance)), self._stream()), "sample")
+        return out
+
+
+_OPS = None
+
+
+def get_ops(verbose: bool = True) -> Ops:
+    """The extension's call table.  Raises if there is no CUDA device or the library cannot be built."""
+    global _OPS
+    if _OPS is None:
+        if not torch.cuda.is_available():
+            raise BuildError("no CUDA device: this library runs on a B200 only and has no other path")
+        _OPS = Ops(load(verbose=verbose))
+    return _OPS

@@ -1,0 +1,146 @@
+// Row-wise kernels: embedding gather, row gather, RMSNorm with and without the residual
+// add, SwiGLU, and the end-of-step length update.  T is the activation type (float or
+// bfloat16), W the norm weight's type (a weight stored in 32-bit stays 32-bit).
+//
+// Formulas of the reference: engine/kernels/rmsnorm.py:31-45 (norm: 32-bit mean of squares,
+// the normalised value rounded to T before the weight multiply),
+// engine/kernels/add_rmsnorm.py:21-29 (sum rounded to T, stored, then normed),
+// engine/kernels/swiglu.py:21-24 (silu in 32-bit, rounded, times up, rounded).
+#include "common.cuh"
+
+template <class T>
+__global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table, T* __restrict__ out,
+                             int hidden, int vocab, int* status) {
+    const int row = blockIdx.x;
+    int tok = tokens[row];
+    if (tok < 0 || tok >= vocab) {
+        if (threadIdx.x == 0) atomicOr(status, SB_STATUS_BAD_TOKEN);
+        tok = 0;
+    }
+    const T* src = table + (long long)tok * hidden;
+    T* dst = out + (long long)row * hidden;
+    for (int c = threadIdx.x; c < hidden; c += blockDim.x) dst[c] = src[c];
+}
+
+template <class T>
+__global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out, int width) {
+    const T* src = x + (long long)rows[blockIdx.x] * width;
+    T* dst = out + (long long)blockIdx.x * width;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
+}
+
+// One block per row.  ADD: x <- T(x + delta) first.
+template <class T, class W, bool ADD>
+__global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, const W* __restrict__ weight,
+                               T* __restrict__ out, int width, float eps) {
+    __shared__ float red[33];
+    T* xr = x + (long long)blockIdx.x * width;
+    const T* dr = ADD ? delta + (long long)blockIdx.x * width : nullptr;
+    T* yr = out + (long long)blockIdx.x * width;
+    float ss = 0.f;
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        float v = to_f<T>(xr[c]);
+        if (ADD) {
+            v = rnd<T>(__fadd_rn(v, to_f<T>(dr[c])));
+            xr[c] = from_f<T>(v);
+        }
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)width + eps);
+    for (int c = threadIdx.x; c < width; c += blockDim.x) {
+        const float n = rnd<T>(__fmul_rn(to_f<T>(xr[c]), rstd));
+        yr[c] = from_f<T>(__fmul_rn(n, to_f<W>(weight[c])));
+    }
+}
+
+template <class T>
+__global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
+    const long long row = blockIdx.x;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= inter) return;
+    const float g = to_f<T>(gu[row * 2 * inter + c]);
+    const float u = to_f<T>(gu[row * 2 * inter + inter + c]);
+    const float s = rnd<T>(g / (1.0f + expf(-g)));
+    out[row * inter + c] = from_f<T>(__fmul_rn(s, u));
+}
+
+__global__ void advance_lengths_kernel(SbBatch b, int* lengths) {
+    const int s = blockIdx.x * blockDim.x + threadIdx.x;
+    if (s >= b.n_seqs) return;
+    const int slot = b.seq_slot[s];
+    if (slot != b.null_slot) lengths[slot] += b.cu_q[s + 1] - b.cu_q[s];
+}
+
+static inline int row_threads(int width) {
+    int t = 32;
+    while (t < 256 && t * 4 < width) t <<= 1;
+    return t;
+}
+
+extern "C" {
+
+int sb_embed(int dtype, const int* tokens, const void* table, void* out, int rows, int hidden, int vocab, int* status,
+             cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    if (dtype == SB_F32)
+        embed_kernel<float><<<rows, row_threads(hidden), 0, stream>>>(tokens, (const float*)table, (float*)out, hidden, vocab, status);
+    else
+        embed_kernel<__nv_bfloat16><<<rows, row_threads(hidden), 0, stream>>>(tokens, (const __nv_bfloat16*)table,
+                                                                                (__nv_bfloat16*)out, hidden, vocab, status);
+    SB_LAUNCH_CHECK();
+}
+
+int sb_gather_rows(int dtype, const void* x, const int* rows, void* out, int n_rows, int width, cudaStream_t stream) {
+    if (n_rows <= 0) return 0;
+    if (dtype == SB_F32)
+        gather_rows_kernel<float><<<n_rows, row_threads(width), 0, stream>>>((const float*)x, rows, (float*)out, width);
+    else
+        gather_rows_kernel<__nv_bfloat16><<<n_rows, row_threads(width), 0, stream>>>((const __nv_bfloat16*)x, rows,
+                                                                                      (__nv_bfloat16*)out, width);
+    SB_LAUNCH_CHECK();
+}
+
+// x [rows, width] (updated in place when delta is given), weight [width] of dtype wdtype, out [rows, width].
+int sb_rmsnorm(int dtype, int wdtype, void* x, const void* delta, const void* weight, void* out, int rows, int width,
+               float eps, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    const int th = row_threads(width);
+#define SB_NORM(T, W)                                                                                             \
+    do {                                                                                                          \
+        if (delta)                                                                                                \
+            rmsnorm_kernel<T, W, true><<<rows, th, 0, stream>>>((T*)x, (const T*)delta, (const W*)weight, (T*)out, width, eps); \
+        else                                                                                                      \
+            rmsnorm_kernel<T, W, false><<<rows, th, 0, stream>>>((T*)x, nullptr, (const W*)weight, (T*)out, width, eps);        \
+    } while (0)
+    if (dtype == SB_F32) {
+        if (wdtype != SB_F32) return (int)cudaErrorInvalidValue;
+        SB_NORM(float, float);
+    } else if (wdtype == SB_F32) {
+        SB_NORM(__nv_bfloat16, float);
+    } else {
+        SB_NORM(__nv_bfloat16, __nv_bfloat16);
+    }
+#undef SB_NORM
+    SB_LAUNCH_CHECK();
+}
+
+int sb_swiglu(int dtype, const void* gu, void* out, int rows, int inter, cudaStream_t stream) {
+    if (rows <= 0) return 0;
+    dim3 grid(rows, (inter + 255) / 256);
+    if (dtype == SB_F32)
+        swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, inter);
+    else
+        swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter);
+    SB_LAUNCH_CHECK();
+}
+
+int sb_advance_lengths(SbBatch b, int* lengths, cudaStream_t stream) {
+    if (b.n_seqs <= 0) return 0;
+    advance_lengths_kernel<<<(b.n_seqs + 127) / 128, 128, 0, stream>>>(b, lengths);
+    SB_LAUNCH_CHECK();
+}
+
+const char* sb_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
+
+}  // extern "C"

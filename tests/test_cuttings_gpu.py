@@ -1,0 +1,23 @@
+"""The engine on the GPU against the plain implementation, in every way of cutting the work."""
+
+import pytest
+
+from conftest import TINY, random_tokens
+from helpers import assert_close, make_session, plain_logits, run_ragged_batches, run_tail_by_one, run_whole
+
+pytestmark = pytest.mark.gpu
+LENGTHS = (5, 150, 77, 1, 64, 65, 33)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", list(TINY))
+def test_every_cutting_matches_plain(tiny_folders, name, dtype):
+    folder = tiny_folders[name]
+    seqs = random_tokens(TINY[name]["vocab_size"], LENGTHS, seed=11)
+    ref = plain_logits(folder, seqs, dtype)
+    sess = make_session(folder, dtype, max_tokens=64 * 10, max_seqs=4, max_step_tokens=48)
+    assert_close(run_whole(sess, seqs), ref, dtype, "alone and whole")
+    assert_close(run_whole(sess, seqs[:3], together=True), ref[:3], dtype, "one ragged step")
+    assert_close(run_tail_by_one(sess, seqs), ref, dtype, "tail one by one")
+    assert_close(run_ragged_batches(sess, seqs, batch_size=3), ref, dtype, "ragged batches")
+    assert sess.cache.slots.n_held == 0

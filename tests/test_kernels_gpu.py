@@ -1,0 +1,179 @@
+"""Each CUDA kernel alone against its plain torch restatement, at sizes other than the models'."""
+
+import math
+
+import pytest
+import torch
+
+from emulated_ops import EmulatedOps
+from starter_b200.cache import Cache, KVRequest
+from starter_b200.engine.context import Runtime, StepContext
+
+pytestmark = pytest.mark.gpu
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+@pytest.fixture(scope="module")
+def ops():
+    from starter_b200.csrc.ops import get_ops
+    return get_ops(verbose=False)
+
+
+@pytest.fixture(scope="module")
+def ref():
+    return EmulatedOps()
+
+
+def rand(shape, dtype, seed, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(shape, generator=g) * scale).to(dtype).cuda()
+
+
+def close(got, want, dtype, what, rel=None):
+    rel = rel if rel is not None else (2e-5 if dtype == torch.float32 else 1.6e-2)
+    scale = float(want.float().abs().max()) + 1e-30
+    err = float((got.float() - want.float()).abs().max())
+    assert err <= rel * scale, f"{what}: {err:.3g} > {rel * scale:.3g}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed_and_gather(ops, ref, dtype):
+    table = rand((301, 72), dtype, 0)
+    tokens = torch.tensor([5, 300, 0, 17, 5], dtype=torch.int32).cuda()
+    status = torch.zeros(1, dtype=torch.int32).cuda()
+    assert torch.equal(ops.embed(tokens, table, status), ref.embed(tokens, table, status.clone()))
+    assert int(status) == 0
+    bad = torch.tensor([5, 301, -1], dtype=torch.int32).cuda()
+    ops.embed(bad, table, status)
+    assert int(status) == 1
+    rows = torch.tensor([4, 0, 4, 2], dtype=torch.int32).cuda()
+    x = rand((5, 72), dtype, 1)
+    assert torch.equal(ops.gather_rows(x, rows), x[rows.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [16, 200, 2560, 5000])
+def test_rmsnorm(ops, ref, dtype, width):
+    x = rand((7, width), dtype, 2, 3.0)
+    w = (1 + 0.1 * rand((width,), torch.float32, 3)).to(dtype)
+    close(ops.rmsnorm(x, w, 1e-5), ref.rmsnorm(x, w, 1e-5), dtype, "rmsnorm")
+    d = rand((7, width), dtype, 4)
+    x1, x2 = x.clone(), x.clone()
+    y1, y2 = ops.add_rmsnorm(x1, d, w, 1e-6), ref.add_rmsnorm(x2, d, w, 1e-6)
+    assert torch.equal(x1, x2), "residual sum"
+    close(y1, y2, dtype, "add_rmsnorm")
+    if dtype == torch.bfloat16:  # a norm weight stored in 32-bit stays 32-bit
+        close(ops.rmsnorm(x, w.float(), 1e-5), ref.rmsnorm(x, w.float(), 1e-5), dtype, "rmsnorm, 32-bit weight")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_swiglu(ops, ref, dtype):
+    gu = rand((5, 2 * 331), dtype, 5, 2.0)
+    close(ops.swiglu(gu), ref.swiglu(gu), dtype, "swiglu", rel=1e-6 if dtype == torch.float32 else 8e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 389, 96), (5, 70, 33), (130, 257, 160), (64, 1000, 4096), (300, 512, 1024)])
+def test_linear(ops, ref, dtype, shape):
+    M, N, K = shape
+    a, w = rand((M, K), dtype, 6), rand((N, K), dtype, 7, 0.05)
+    close(ops.linear(a, w), ref.linear(a, w), dtype, "linear")
+    close(ops.linear(a, w, out_float32=True), ref.linear(a, w, out_float32=True), dtype, "linear, 32-bit out",
+          rel=2e-5 if dtype == torch.float32 else 2e-3)
+
+
+def make_ctx(cache, ops, slots, q_lens, dtype):
+    rt = Runtime(dtype=dtype, device=torch.device("cuda"), ops=ops)
+    cu = [0]
+    row_seq = []
+    for b, n in enumerate(q_lens):
+        cu.append(cu[-1] + n)
+        row_seq += [b] * n
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32).cuda()
+    return StepContext(runtime=rt, cache=cache, n_seqs=len(slots), n_rows=cu[-1], max_q_len=max(q_lens),
+                       kv_bound=max(cache.lengths_host[s] + n for s, n in zip(slots, q_lens)), seq_slot=i32(slots),
+                       cu_q=i32(cu), row_seq=i32(row_seq), lengths=cache.lengths,
+                       status=torch.zeros(1, dtype=torch.int32).cuda())
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(6, 3, 48, None), (4, 1, 16, 9), (8, 8, 128, None), (2, 2, 80, 70)])
+def test_store_and_attention(ops, ref, dtype, heads, kv_heads, head_dim, window):
+    """Two steps over three sequences of unequal length: rope + store + attention against the
+    torch restatement working on a second, identical cache."""
+    req = KVRequest(kv_heads, head_dim, window)
+    caches = [Cache([req], n_slots=4, max_tokens=64 * 12, dtype=dtype, device="cuda", max_step_tokens=100) for _ in range(2)]
+    half = head_dim // 2
+    ang = torch.arange(400, dtype=torch.float32)[:, None] / (10000.0 ** (torch.arange(half).float() / half))[None]
+    rotary = (ang.cos().to(dtype).cuda(), ang.sin().to(dtype).cuda(), head_dim)
+    qn = (1 + 0.1 * rand((head_dim,), torch.float32, 8)).to(dtype)
+    kn = (1 + 0.1 * rand((head_dim,), torch.float32, 9)).to(dtype)
+    slots = [[c.alloc() for _ in range(3)] for c in caches]
+    assert slots[0] == slots[1]
+    for step, q_lens in enumerate([(70, 3, 100), (1, 1, 5)]):
+        outs = []
+        for c, o in zip(caches, (ops, ref)):
+            for s, n in zip(slots[0], q_lens):
+                c.reserve(s, c.lengths_host[s] + n)
+            c.flush()
+            ctx = make_ctx(c, ops, slots[0], q_lens, dtype)
+            qkv = rand((sum(q_lens), (heads + 2 * kv_heads) * head_dim), dtype, 20 + step)
+            q = o.qk_norm_rope_store(ctx, qkv, c.layers[0], heads, kv_heads, head_dim, qn, kn, 1e-6, rotary)
+            a = o.attention(ctx, q, c.layers[0], heads, 1.0 / math.sqrt(head_dim), window)
+            o.advance_lengths(ctx)
+            for s, n in zip(slots[0], q_lens):
+                c.advance_host(s, n)
+            assert int(ctx.status) == 0
+            outs.append((q, a))
+        close(outs[0][0], outs[1][0], dtype, f"q after norm and rope, step {step}", rel=1e-5 if dtype == torch.float32 else 8e-3)
+        close(outs[0][1], outs[1][1], dtype, f"attention, step {step}")
+        close(caches[0].groups[0].k, caches[1].groups[0].k, dtype, "stored keys", rel=1e-5 if dtype == torch.float32 else 8e-3)
+        assert torch.equal(caches[0].groups[0].v, caches[1].groups[0].v), "stored values"
+        assert torch.equal(caches[0].lengths, caches[1].lengths)
+
+
+def test_attention_finds_a_far_key(ops):
+    """One key among hundreds is made to stand out: the output must be its value."""
+    dtype, heads, head_dim = torch.float32, 2, 32
+    cache = Cache([KVRequest(1, head_dim, None)], n_slots=2, max_tokens=64 * 8, dtype=dtype, device="cuda")
+    slot = cache.alloc()
+    n = 300
+    cache.reserve(slot, n)
+    cache.flush()
+    ctx = make_ctx(cache, ops, [slot], [n], dtype)
+    qkv = rand((n, (heads + 2) * head_dim), dtype, 30, 0.1)
+    qkv[:, heads * head_dim:(heads + 1) * head_dim] = 0.01 * rand((n, head_dim), dtype, 31)
+    qkv[37, heads * head_dim:(heads + 1) * head_dim] = 10.0  # key 37 is large ...
+    qkv[-1, :heads * head_dim] = 10.0                        # ... and the last query points at it
+    q = ops.qk_norm_rope_store(ctx, qkv, cache.layers[0], heads, 1, head_dim, None, None, 0.0, None)
+    a = ops.attention(ctx, q, cache.layers[0], heads, 1.0, None)
+    want = qkv[37, (heads + 1) * head_dim:]
+    assert torch.allclose(a[-1, :head_dim], want, atol=1e-5) and torch.allclose(a[-1, head_dim:], want, atol=1e-5)
+
+
+def test_argmax_ties_and_sampling(ops):
+    logits = rand((5, 1000), torch.float32, 40)
+    logits[1, 700] = logits[1, 20] = 50.0   # equal maxima: the lower index wins
+    logits[2, 999] = 60.0
+    got = ops.argmax(logits).cpu()
+    want = logits.cpu().argmax(-1)
+    want[1] = 20
+    assert got.tolist() == want.tolist()
+    assert ops.argmax(rand((3, 151936), torch.float32, 41)).tolist() == rand((3, 151936), torch.float32, 41).argmax(-1).tolist()
+
+
+@pytest.mark.parametrize("top_k", [0, 1, 7, 50])
+def test_sampling_matches_plain(ops, top_k):
+    from plain import qwen3_plain as plain
+    vocab, rows = 389, 16
+    logits = rand((rows, vocab), torch.float32, 50, 2.0)
+    logits[3, 100] = logits[3, 200] = logits[3, 300] = float(logits[3].max()) + 0.5  # ties at the edge of the kept set
+    req = torch.arange(rows, dtype=torch.int32).cuda() + 5
+    steps = torch.full((rows,), 3, dtype=torch.int32).cuda()
+    got = ops.sample(logits, 0.8, top_k, 1234, req, steps, advance=True).tolist()
+    assert steps.tolist() == [4] * rows
+    for r in range(rows):
+        u = plain.uniform_from_counter(1234, 5 + r, 3)
+        tok, margin = plain.sample(logits[r].cpu(), 0.8, top_k, u)
+        if margin > 1e-5:  # a draw this far from an edge cannot be flipped by 32-bit rounding
+            assert got[r] == tok, f"row {r}: {got[r]} != {tok} (margin {margin:.2g})"
