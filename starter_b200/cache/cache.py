@@ -240,6 +240,13 @@ class Cache:
             if isinstance(g, KVGroup):
                 g.reserve(slot, n_tokens)
 
+    def assume_length(self, slot: int, n_tokens: int) -> None:
+        """Declare that the slot already holds ``n_tokens`` tokens (pages reserved, contents as they
+        are).  For benchmarks that start from a synthetic context instead of a real prompt."""
+        self.reserve(slot, n_tokens)
+        self.lengths_host[slot] = int(n_tokens)
+        self._dirty_lengths.add(slot)
+
     def advance_host(self, slot: int, n: int) -> None:
         """Mirror on the host what the step's kernel did to the device lengths."""
         self.lengths_host[slot] += n

@@ -54,6 +54,7 @@ class Ops:
 
     def __init__(self, lib: ctypes.CDLL):
         self.lib = lib
+        self.launches = 0  # kernels of this library launched so far (cuBLAS calls are not counted)
         lib.sb_error_string.restype = ctypes.c_char_p
         lib.sb_error_string.argtypes = [c_int]
         sig = {
@@ -82,6 +83,7 @@ class Ops:
         return c_void_p(torch.cuda.current_stream().cuda_stream)
 
     def _check(self, code: int, what: str) -> None:
+        self.launches += 1
         if code:
             raise KernelError(f"{what}: {self.lib.sb_error_string(code).decode()} (code {code})")
 

@@ -145,3 +145,15 @@ class EmulatedOps:
 
     def argmax(self, logits):
         return logits.float().argmax(dim=-1).to(torch.int32)
+
+    def sample(self, logits, temperature, top_k, seed, request_ids, steps, advance=False):
+        from plain import qwen3_plain as plain
+        out = []
+        for r in range(logits.shape[0]):
+            req = int(request_ids[r]) if request_ids is not None else r
+            step = int(steps[r]) if steps is not None else 0
+            tok, _ = plain.sample(logits[r].float().cpu(), temperature, top_k, plain.uniform_from_counter(seed, req, step))
+            out.append(tok)
+        if advance and steps is not None:
+            steps += 1
+        return torch.tensor(out, dtype=torch.int32, device=logits.device)

@@ -1,0 +1,93 @@
+"""Generation through the entry point on the GPU: greedy and sampled, with CUDA graphs and
+without, against the plain loop; long decoding; stop tokens; slots used again."""
+
+import pytest
+import torch
+
+from conftest import TINY, random_tokens
+from plain import qwen3_plain as plain
+from starter_b200.engine import Engine
+
+pytestmark = pytest.mark.gpu
+
+
+def tokens_agree(got, want, cfg, tensors, prompts, dtype, margin):
+    """Token-exact, except where the plain logits hold a near-tie that rounding may flip:
+    then the engine's token must be within ``margin`` of the plain maximum, and the
+    comparison goes on along the engine's own sequence."""
+    for b, (g, w) in enumerate(zip(got, want)):
+        if g == w:
+            continue
+        assert len(g) == len(w)
+        seq = list(prompts[b])
+        for t, tok in enumerate(g):
+            logits = plain.forward(cfg, tensors, seq, dtype)[-1]
+            gap = float(logits.max() - logits[tok])
+            assert gap <= margin * float(logits.abs().max()), f"request {b}, new token {t}: {tok} is {gap:.3g} below the maximum"
+            seq.append(tok)
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_greedy_tiny_a(tiny_folders, dtype, graphs):
+    prompts = random_tokens(256, (5, 9, 12), seed=3)
+    cfg, tensors = plain.read_folder(tiny_folders["A"])
+    want = plain.generate(cfg, tensors, prompts, 8, dtype)
+    eng = Engine(tiny_folders["A"], dtype=dtype, max_batch=4, max_context=128, use_graphs=graphs)
+    steps = list(eng.generate(prompts, 8))
+    assert len(steps) == 8 and all(len(s) == 3 and None not in s for s in steps)
+    got = [[s[b] for s in steps] for b in range(3)]
+    tokens_agree(got, want, cfg, tensors, prompts, dtype, 1e-4 if dtype == "float32" else 2e-2)
+    again = list(eng.generate(prompts, 8))                                  # second call: state reset
+    assert [[s[b] for s in again] for b in range(3)] == got
+    assert eng.session.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+def test_sampled_tiny_b(tiny_folders, graphs):
+    prompts = random_tokens(389, (1, 7, 16, 23), seed=4)
+    eng = Engine(tiny_folders["B"], dtype="float32", max_batch=4, max_context=128, use_graphs=graphs)
+    got = eng.generate_all(prompts, 10, temperature=0.8, seed=99)
+    # The draw is a function of the logits: feed the engine's own sequences to the plain model and
+    # redo every draw from the plain logits; a draw near an edge of the running sum may differ.
+    cfg, tensors = plain.read_folder(tiny_folders["B"])
+    for r, (p, new) in enumerate(zip(prompts, got)):
+        assert len(new) == 10
+        seq = list(p)
+        for step, tok in enumerate(new):
+            logits = plain.forward(cfg, tensors, seq, "float32")[-1]
+            want, margin = plain.sample(logits, 0.8, 0, plain.uniform_from_counter(99, r, step))
+            if margin > 1e-4:
+                assert tok == want, f"request {r} step {step}: {tok} != {want} (margin {margin:.2g})"
+            seq.append(tok)
+    solo = Engine(tiny_folders["B"], dtype="float32", max_batch=1, max_context=128, use_graphs=graphs)
+    assert solo.generate_all(prompts, 10, temperature=0.8, seed=99) == got
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graphs_and_eager_agree_over_a_long_decode(tiny_folders, dtype):
+    """200 new tokens cross several cache pages; both ways of running the steps give the same tokens."""
+    prompts = random_tokens(301, (3, 50, 64), seed=7)
+    outs = []
+    for graphs in (False, True):
+        eng = Engine(tiny_folders["W"], dtype=dtype, max_batch=4, max_context=320, use_graphs=graphs)
+        outs.append(eng.generate_all(prompts, 200))
+    assert outs[0] == outs[1]
+    cfg, tensors = plain.read_folder(tiny_folders["W"])
+    if dtype == "float32":
+        want = plain.generate(cfg, tensors, prompts[:1], 200, dtype)
+        tokens_agree(outs[0][:1], want, cfg, tensors, prompts[:1], dtype, 1e-4)
+
+
+def test_stop_tokens_and_slot_reuse(tiny_folders):
+    prompts = random_tokens(256, (5, 9, 12, 30, 2), seed=3)
+    cfg, tensors = plain.read_folder(tiny_folders["A"])
+    free_run = plain.generate(cfg, tensors, prompts, 12, "float32")
+    stop = {free_run[0][2], free_run[3][6]}
+    want = plain.generate(cfg, tensors, prompts, 12, "float32", stop_token_ids=stop)
+    for graphs in (False, True):
+        eng = Engine(tiny_folders["A"], dtype="float32", max_batch=2, max_context=128, use_graphs=graphs)
+        got = eng.generate_all(prompts, 12, stop_token_ids=stop)
+        tokens_agree(got, want, cfg, tensors, prompts, "float32", 1e-4)
+        assert eng.session.cache.slots.n_held == 0
+        eng.session.cache.check()
