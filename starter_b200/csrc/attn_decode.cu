@@ -1,0 +1,309 @@
+// Decode attention over the paged cache: one new token per sequence, grouped query heads,
+// keys split across thread blocks, partial results merged by the last block to finish.
+//
+// Reference: engine/kernels/attention.py:24-114 (split-K flash decoding: all G = heads /
+// kv_heads query heads of a key/value head share one program so that keys and values are
+// read once per group; scores, maximum, exp and sum in 32-bit; probabilities rounded to
+// bfloat16 before they meet V; one division at the end; partial (m, l, acc) triples merged).
+//
+// Layout of the work.  Grid (sequence, kv head, split).  A block has four warps; warp w owns
+// the keys 16w..16w+15 of every cache page (64 keys) in the block's range of pages, brings them
+// in with its own cp.async pipeline, and keeps its own running (m, l, acc): softmax states
+// merge exactly, so the warps never wait for one another until the end.  The tensor cores
+// (mma.sync m16n8k16, bfloat16 in, 32-bit accumulate) see the G query heads as the rows of a
+// 16-row tile.  The split count depends on shapes only; the pages are divided among the
+// splits on the device from the sequence's own length, so a graph replay stays valid as the
+// sequence grows.  With more than one split each block leaves its partial result in scratch
+// memory and the last one to arrive (an atomic counter per sequence and kv head) merges them.
+#include "common.cuh"
+
+#define AD_WARPS 4
+#define AD_STAGES 3
+#define AD_KEYS_PER_WARP (SB_PAGE / AD_WARPS)  // 16
+
+__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
+    const unsigned int s = (unsigned int)__cvta_generic_to_shared(smem_dst);
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem_src));
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
+template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
+
+__device__ __forceinline__ void ldmatrix_x4(unsigned int (&r)[4], const void* smem_ptr) {
+    const unsigned int s = (unsigned int)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(unsigned int (&r)[4], const void* smem_ptr) {
+    const unsigned int s = (unsigned int)__cvta_generic_to_shared(smem_ptr);
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned int (&a)[4], unsigned int b0, unsigned int b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ unsigned int pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<unsigned int*>(&v);
+}
+
+// Byte offset of 16-byte chunk `chunk` of row `row` in a [rows][D] bfloat16 tile whose chunks
+// are XOR-swizzled by the row so that ldmatrix reads eight rows without bank conflicts.
+template <int D> __device__ __forceinline__ int tile_off(int row, int chunk) {
+    return row * (D * 2) + ((chunk ^ (row & 7)) << 4);
+}
+
+template <int D>
+__global__ void __launch_bounds__(AD_WARPS * 32)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, SbBatch batch, SbKV kv,
+                   int n_heads, float scale_log2, int window, int n_splits, float* __restrict__ partial,
+                   int* __restrict__ counters) {
+    constexpr int CH = D / 8;                              // 16-byte chunks per row
+    constexpr int SLICE = AD_KEYS_PER_WARP * D * 2;        // bytes of one warp's keys (or values) of a page
+    constexpr int NT = D / 8;                              // output n-tiles of 8 columns
+    extern __shared__ __align__(128) unsigned char smem[];
+    __shared__ int s_is_last;
+    unsigned char* q_s = smem;                             // [16][D] bfloat16
+    unsigned char* pipe = smem + 16 * D * 2;               // [warp][stage][K slice | V slice]
+
+    const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int G = n_heads / kv.n_kv_heads;
+    const int slot = batch.seq_slot[seq];
+    const int row = batch.cu_q[seq];
+    const int pos = batch.lengths[slot];                   // the new token's position; keys 0..pos are visible
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first_page = lo / SB_PAGE, last_page = pos / SB_PAGE;
+    const int n_pages = last_page - first_page + 1;
+    const int per_split = (n_pages + n_splits - 1) / n_splits;
+    const int p_begin = first_page + split * per_split;
+    const int p_end = min(p_begin + per_split, last_page + 1);
+    const int my_pages = max(p_end - p_begin, 0);
+
+    // Query heads of this kv head as rows of a 16-row tile, zero beyond G.
+    for (int i = tid; i < 16 * CH; i += AD_WARPS * 32) {
+        const int r = i / CH, c = i % CH;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < G) v = *reinterpret_cast<const uint4*>(q + ((long long)row * n_heads + kvh * G + r) * D + c * 8);
+        *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
+    }
+    __syncthreads();
+    unsigned int qf[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+        ldmatrix_x4(qf[ks], q_s + tile_off<D>((lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+
+    unsigned char* my_pipe = pipe + warp * (AD_STAGES * 2 * SLICE);
+    const __nv_bfloat16* kbase = (const __nv_bfloat16*)kv.k;
+    const __nv_bfloat16* vbase = (const __nv_bfloat16*)kv.v;
+    const int* table = kv.table + (long long)slot * kv.table_width;
+
+    auto issue = [&](int i) {  // bring this warp's keys and values of the block's i-th page into stage i % STAGES
+        if (i < my_pages) {
+            int lp = p_begin + i;
+            if (kv.ring_pages) lp %= kv.ring_pages;
+            const int page = max(table[lp], 0);  // an unreserved page was flagged when the row was stored
+            const long long base = (((long long)page * kv.n_kv_heads + kvh) * SB_PAGE + warp * AD_KEYS_PER_WARP) * D;
+            unsigned char* ks = my_pipe + (i % AD_STAGES) * 2 * SLICE;
+            unsigned char* vs = ks + SLICE;
+#pragma unroll
+            for (int j = lane; j < AD_KEYS_PER_WARP * CH; j += 32) {
+                const int r = j / CH, c = j % CH;
+                cp_async_16(ks + tile_off<D>(r, c), kbase + base + r * D + c * 8);
+                cp_async_16(vs + tile_off<D>(r, c), vbase + base + r * D + c * 8);
+            }
+        }
+        cp_async_commit();
+    };
+
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+
+#pragma unroll
+    for (int i = 0; i < AD_STAGES - 1; ++i) issue(i);
+    for (int i = 0; i < my_pages; ++i) {
+        issue(i + AD_STAGES - 1);
+        cp_async_wait<AD_STAGES - 1>();
+        __syncwarp();
+        const unsigned char* ks = my_pipe + (i % AD_STAGES) * 2 * SLICE;
+        const unsigned char* vs = ks + SLICE;
+
+        float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int kk = 0; kk < D / 16; ++kk) {
+            unsigned int b[4];
+            ldmatrix_x4(b, ks + tile_off<D>((lane & 7) + (lane >> 4) * 8, kk * 2 + ((lane >> 3) & 1)));
+            mma_bf16(s0, qf[kk], b[0], b[1]);
+            mma_bf16(s1, qf[kk], b[2], b[3]);
+        }
+        // keys of this thread's columns: n0 + {0,1} in tile 0, n0 + 8 + {0,1} in tile 1
+        const int n0 = (p_begin + i) * SB_PAGE + warp * AD_KEYS_PER_WARP + (lane & 3) * 2;
+        const bool v00 = n0 >= lo && n0 <= pos, v01 = n0 + 1 >= lo && n0 + 1 <= pos;
+        const bool v10 = n0 + 8 >= lo && n0 + 8 <= pos, v11 = n0 + 9 >= lo && n0 + 9 <= pos;
+        float t[2][4];
+        t[0][0] = v00 ? s0[0] * scale_log2 : -INFINITY;
+        t[0][1] = v01 ? s0[1] * scale_log2 : -INFINITY;
+        t[0][2] = v10 ? s1[0] * scale_log2 : -INFINITY;
+        t[0][3] = v11 ? s1[1] * scale_log2 : -INFINITY;
+        t[1][0] = v00 ? s0[2] * scale_log2 : -INFINITY;
+        t[1][1] = v01 ? s0[3] * scale_log2 : -INFINITY;
+        t[1][2] = v10 ? s1[2] * scale_log2 : -INFINITY;
+        t[1][3] = v11 ? s1[3] * scale_log2 : -INFINITY;
+        float alpha[2];
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            float mx = fmaxf(fmaxf(t[h][0], t[h][1]), fmaxf(t[h][2], t[h][3]));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+            mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+            const float m_new = fmaxf(m[h], mx);
+            const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+            alpha[h] = exp2f(m[h] - m_safe);
+            float sum = 0.f;
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                t[h][e] = exp2f(t[h][e] - m_safe);
+                sum += t[h][e];
+            }
+            l[h] = l[h] * alpha[h] + sum;
+            m[h] = m_new;
+        }
+        unsigned int pf[4];
+        pf[0] = pack_bf16(t[0][0], t[0][1]);
+        pf[1] = pack_bf16(t[1][0], t[1][1]);
+        pf[2] = pack_bf16(t[0][2], t[0][3]);
+        pf[3] = pack_bf16(t[1][2], t[1][3]);
+#pragma unroll
+        for (int j = 0; j < NT; j += 2) {
+            unsigned int b[4];
+            ldmatrix_x4_trans(b, vs + tile_off<D>((lane & 7) + ((lane >> 3) & 1) * 8, j + (lane >> 4)));
+            acc[j][0] *= alpha[0]; acc[j][1] *= alpha[0]; acc[j][2] *= alpha[1]; acc[j][3] *= alpha[1];
+            acc[j + 1][0] *= alpha[0]; acc[j + 1][1] *= alpha[0]; acc[j + 1][2] *= alpha[1]; acc[j + 1][3] *= alpha[1];
+            mma_bf16(acc[j], pf, b[0], b[1]);
+            mma_bf16(acc[j + 1], pf, b[2], b[3]);
+        }
+        __syncwarp();
+    }
+    cp_async_wait<0>();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
+    __syncthreads();  // every warp is done with the pipeline's memory; it now holds the warps' states
+
+    // Warp states to shared memory: acc [warp][16][D] floats, then m and l [warp][16].
+    float* w_acc = reinterpret_cast<float*>(pipe);
+    float* w_m = w_acc + AD_WARPS * 16 * D;
+    float* w_l = w_m + AD_WARPS * 16;
+    {
+        const int r0 = lane >> 2, c0 = (lane & 3) * 2;
+#pragma unroll
+        for (int j = 0; j < NT; ++j) {
+            float* dst = w_acc + (warp * 16 + r0) * D + j * 8 + c0;
+            dst[0] = acc[j][0]; dst[1] = acc[j][1];
+            dst[8 * D] = acc[j][2]; dst[8 * D + 1] = acc[j][3];
+        }
+        if ((lane & 3) == 0) {
+            w_m[warp * 16 + r0] = m[0]; w_m[warp * 16 + r0 + 8] = m[1];
+            w_l[warp * 16 + r0] = l[0]; w_l[warp * 16 + r0 + 8] = l[1];
+        }
+    }
+    __syncthreads();
+
+    const long long part_stride = D + 2;
+    for (int i = tid; i < G * D; i += AD_WARPS * 32) {
+        const int r = i / D, d = i % D;
+        float M = -INFINITY;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) M = fmaxf(M, w_m[w * 16 + r]);
+        float o = 0.f, L = 0.f;
+#pragma unroll
+        for (int w = 0; w < AD_WARPS; ++w) {
+            const float mw = w_m[w * 16 + r];
+            const float wgt = mw == -INFINITY ? 0.f : exp2f(mw - M);
+            o += w_acc[(w * 16 + r) * D + d] * wgt;
+            L += w_l[w * 16 + r] * wgt;
+        }
+        const int head = kvh * G + r;
+        if (n_splits == 1) {
+            out[((long long)row * n_heads + head) * D + d] = __float2bfloat16_rn(o / L);
+        } else {
+            float* p = partial + (((long long)seq * n_heads + head) * n_splits + split) * part_stride;
+            p[d] = o;
+            if (d == 0) { p[D] = M; p[D + 1] = L; }
+        }
+    }
+    if (n_splits == 1) return;
+
+    // The last block of this (sequence, kv head) to get here merges the splits.
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+        const int prev = atomicAdd(&counters[seq * kv.n_kv_heads + kvh], 1);
+        s_is_last = prev == n_splits - 1;
+    }
+    __syncthreads();
+    if (!s_is_last) return;
+    __threadfence();
+    for (int i = tid; i < G * D; i += AD_WARPS * 32) {
+        const int r = i / D, d = i % D;
+        const int head = kvh * G + r;
+        const float* p = partial + ((long long)seq * n_heads + head) * n_splits * part_stride;
+        float M = -INFINITY;
+        for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(p + s * part_stride + D));
+        float o = 0.f, L = 0.f;
+        for (int s = 0; s < n_splits; ++s) {
+            const float ms = __ldcg(p + s * part_stride + D);
+            const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - M);
+            o += __ldcg(p + s * part_stride + d) * wgt;
+            L += __ldcg(p + s * part_stride + D + 1) * wgt;
+        }
+        out[((long long)row * n_heads + head) * D + d] = __float2bfloat16_rn(o / L);
+    }
+    if (tid == 0) counters[seq * kv.n_kv_heads + kvh] = 0;  // ready for the next launch
+}
+
+template <int D> static int launch_decode(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale,
+                                          int window, int n_splits, float* partial, int* counters, cudaStream_t stream) {
+    const int pipe_bytes = AD_WARPS * AD_STAGES * 2 * AD_KEYS_PER_WARP * D * 2;
+    const int merge_bytes = (AD_WARPS * 16 * D + 2 * AD_WARPS * 16) * 4;
+    const int smem = 16 * D * 2 + (pipe_bytes > merge_bytes ? pipe_bytes : merge_bytes);
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    dim3 grid(batch.n_seqs, kv.n_kv_heads, n_splits);
+    attn_decode_kernel<D><<<grid, AD_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv,
+                                                                 n_heads, scale * 1.4426950408889634f, window, n_splits,
+                                                                 partial, counters);
+    return (int)cudaGetLastError();
+}
+
+extern "C" {
+
+// Floats of scratch the kernel needs for a batch: partial results [seq][head][split][D + 2].
+long long sb_attn_decode_scratch_floats(int n_seqs, int n_heads, int head_dim, int n_splits) {
+    return n_splits > 1 ? (long long)n_seqs * n_heads * n_splits * (head_dim + 2) : 0;
+}
+
+// One new token per sequence (rows == sequences).  q, out [rows, n_heads * head_dim] bfloat16.
+// Takes head_dim 64 or 128 and up to 16 query heads per kv head; anything else is refused.
+// partial: scratch of sb_attn_decode_scratch_floats floats; counters: n_seqs * n_kv_heads ints,
+// zero before the first launch (the kernel leaves them zero).
+int sb_attn_decode(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale, int window, int n_splits,
+                   float* partial, int* counters, cudaStream_t stream) {
+    if (batch.n_seqs <= 0) return 0;
+    if (batch.n_rows != batch.n_seqs || n_heads % kv.n_kv_heads || n_heads / kv.n_kv_heads > 16 || n_splits < 1 ||
+        n_splits > 65535 || kv.n_kv_heads > 65535)
+        return (int)cudaErrorInvalidValue;
+    if (kv.head_dim == 128) return launch_decode<128>(q, out, batch, kv, n_heads, scale, window, n_splits, partial, counters, stream);
+    if (kv.head_dim == 64) return launch_decode<64>(q, out, batch, kv, n_heads, scale, window, n_splits, partial, counters, stream);
+    return (int)cudaErrorInvalidValue;
+}
+
+}  // extern "C"

@@ -67,6 +67,7 @@ class Ops:
             "sb_qk_rope_store": [c_int, c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_int, c_void_p, c_void_p,
                                  c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
             "sb_attention_general": [c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_void_p],
+            "sb_attn_decode": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
             "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
                           c_void_p],
@@ -75,6 +76,8 @@ class Ops:
             fn = getattr(lib, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+        self._scratch = {}
+        self._sm_count = None
 
     # ---- plumbing -----------------------------------------------------------------------
 
@@ -199,9 +202,42 @@ class Ops:
                                               _ptr(ctx.status), self._stream()), "qk_rope_store")
         return q
 
+    def sm_count(self) -> int:
+        if self._sm_count is None:
+            self._sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
+        return self._sm_count
+
+    def decode_splits(self, n_seqs: int, n_kv_heads: int, max_pages: int) -> int:
+        """How many blocks share one (sequence, kv head): enough to give every SM two blocks.
+        A function of shapes only, so that a captured graph stays valid as sequences grow."""
+        want = -(-2 * self.sm_count() // max(n_seqs * n_kv_heads, 1))
+        return max(1, min(want, max_pages, 64))
+
+    def _decode_scratch(self, device, n_seqs, n_heads, n_kv_heads, head_dim, n_splits):
+        key = ("attn_decode", device, n_seqs, n_heads, n_kv_heads, head_dim, n_splits)
+        buf = self._scratch.get(key)
+        if buf is None:
+            floats = max(n_seqs * n_heads * n_splits * (head_dim + 2), 1)
+            buf = (torch.empty(floats, dtype=torch.float32, device=device),
+                   torch.zeros(n_seqs * n_kv_heads, dtype=torch.int32, device=device))
+            self._scratch[key] = buf
+        return buf
+
     def attention(self, ctx, q, layer_cache, n_heads, scale, window):
+        """Causal attention of the step's rows over the layer's cache.  Steps of one token per
+        sequence in bfloat16 with head size 64 or 128 take the split-key decode kernel; everything
+        else takes the general kernel."""
         out = torch.empty_like(q)
-        self._check(self.lib.sb_attention_general(_code(q.dtype), _ptr(q), _ptr(out), self._batch(ctx), self._kv(layer_cache),
+        kv = self._kv(layer_cache)
+        if (q.dtype == torch.bfloat16 and ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and kv.head_dim in (64, 128)
+                and n_heads // kv.n_kv_heads <= 16):
+            g = layer_cache.group
+            n_splits = self.decode_splits(ctx.n_seqs, kv.n_kv_heads, g.table_width)
+            partial, counters = self._decode_scratch(q.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, n_splits)
+            self._check(self.lib.sb_attn_decode(_ptr(q), _ptr(out), self._batch(ctx), kv, n_heads, scale, int(window or 0),
+                                                n_splits, _ptr(partial), _ptr(counters), self._stream()), "attn_decode")
+            return out
+        self._check(self.lib.sb_attention_general(_code(q.dtype), _ptr(q), _ptr(out), self._batch(ctx), kv,
                                                   n_heads, scale, int(window or 0), self._stream()), "attention_general")
         return out
 

@@ -177,3 +177,42 @@ def test_sampling_matches_plain(ops, top_k):
         tok, margin = plain.sample(logits[r].cpu(), 0.8, top_k, u)
         if margin > 1e-5:  # a draw this far from an edge cannot be flipped by 32-bit rounding
             assert got[r] == tok, f"row {r}: {got[r]} != {tok} (margin {margin:.2g})"
+
+
+@pytest.mark.parametrize("splits", [None, 1, 3])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(8, 2, 128, None), (16, 1, 64, None), (6, 3, 64, 100), (4, 4, 128, 700)])
+def test_decode_attention(ops, ref, monkeypatch, heads, kv_heads, head_dim, window, splits):
+    """One new token per sequence over contexts of 0 to 1500 tokens, against the torch restatement;
+    in the longest sequence one far key is made to stand out."""
+    dtype = torch.bfloat16
+    if splits is not None:
+        monkeypatch.setattr(ops, "decode_splits", lambda *a: splits)
+    cache = Cache([KVRequest(kv_heads, head_dim, window)], n_slots=6, max_tokens=64 * 60, dtype=dtype, device="cuda",
+                  max_seq_tokens=1600, max_step_tokens=64)
+    g = cache.groups[0]
+    g.k.copy_(rand(tuple(g.k.shape), dtype, 60))
+    g.v.copy_(rand(tuple(g.v.shape), dtype, 61))
+    lengths = [0, 63, 64, 700, 1500]
+    slots = [cache.alloc() for _ in lengths]
+    for s, n in zip(slots, lengths):
+        cache.assume_length(s, n)
+        cache.reserve(s, n + 1)
+    cache.flush()
+    ctx = make_ctx(cache, ops, slots, [1] * len(lengths), dtype)
+    qkv = rand((len(lengths), (heads + 2 * kv_heads) * head_dim), dtype, 62)
+    if window is None:  # key 37 of the last sequence is large and the new query of head 0 points at it
+        lp, off = 37 // 64, 37 % 64
+        page = int(g.table_host[slots[-1], lp])
+        g.k[0, page, 0, off] = 4.0
+        qkv[-1, :head_dim] = 4.0
+    outs = []
+    for o in (ops, ref):
+        k0, v0 = g.k.clone(), g.v.clone()
+        q = o.qk_norm_rope_store(ctx, qkv, cache.layers[0], heads, kv_heads, head_dim, None, None, 0.0, None)
+        outs.append(o.attention(ctx, q, cache.layers[0], heads, 1.0 / math.sqrt(head_dim), window))
+        g.k.copy_(k0)
+        g.v.copy_(v0)
+    close(outs[0], outs[1], dtype, "decode attention")
+    if window is None:
+        want = g.v[0, int(g.table_host[slots[-1], 0]), 0, 37].float()
+        assert float((outs[0][-1, :head_dim].float() - want).abs().max()) < 0.05 * float(want.abs().max())
