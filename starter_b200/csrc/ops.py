@@ -67,6 +67,8 @@ class Ops:
             "sb_qk_rope_store": [c_int, c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_int, c_void_p, c_void_p,
                                  c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
             "sb_attention_general": [c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_void_p],
+            "sb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                               c_void_p, c_void_p],
             "sb_attn_decode": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
             "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
@@ -160,22 +162,53 @@ class Ops:
 
     # ---- products -----------------------------------------------------------------------
 
+    SKINNY_MAX_ROWS = 16
+
+    def _skinny(self, a, w, n_out, gate_up, out_float32):
+        """The weight-streaming product for a handful of rows (see gemm_skinny.cu)."""
+        M, K = a.shape
+        blocks = -(-n_out // 16)
+        want = max(1, min(-(-4 * self.sm_count() // blocks), -(-K // 1024)))
+        k_per_split = -(-K // want // 128) * 128 if want > 1 else -(-K // 128) * 128
+        n_splits = -(-K // k_per_split)
+        key = ("gemm_skinny", a.device, M > 8, n_out, n_splits, gate_up)
+        buf = self._scratch.get(key)
+        if buf is None:
+            floats = blocks * n_splits * (2 if gate_up else 1) * 16 * (8 if M <= 8 else 16) if n_splits > 1 else 1
+            buf = (torch.empty(floats, dtype=torch.float32, device=a.device),
+                   torch.zeros(blocks, dtype=torch.int32, device=a.device))
+            self._scratch[key] = buf
+        out = torch.empty((M, n_out), dtype=torch.float32 if out_float32 else torch.bfloat16, device=a.device)
+        self._check(self.lib.sb_gemm_skinny(_ptr(a), _ptr(w), _ptr(out), M, n_out, K, n_splits, k_per_split, int(gate_up),
+                                            int(out_float32), _ptr(buf[0]), _ptr(buf[1]), self._stream()), "gemm_skinny")
+        return out
+
     def linear(self, a, w, out_float32=False):
-        """a [M, K] times w [N, K] transposed -> [M, N] in a's dtype, or 32-bit when asked."""
+        """a [M, K] times w [N, K] transposed -> [M, N] in a's dtype, or 32-bit when asked.
+
+        float32: this library's CUDA-core product, always.  bfloat16: the weight-streaming kernel for up
+        to 16 rows, cuBLAS for large products, the CUDA-core product for what is left."""
         M, K = a.shape
         N = w.shape[0]
         if w.shape[1] != K or a.dtype != w.dtype:
             raise KernelError(f"linear: a is {tuple(a.shape)} {a.dtype}, w is {tuple(w.shape)} {w.dtype}")
-        if a.dtype == torch.bfloat16 and M * N * K > self.GENERAL_GEMM_MAX_WORK and K % 8 == 0:
-            if out_float32:
-                return torch.mm(a, w.t(), out_dtype=torch.float32)
-            return torch.mm(a, w.t())
+        if a.dtype == torch.bfloat16 and K % 8 == 0:
+            if M <= self.SKINNY_MAX_ROWS:
+                return self._skinny(a, w, N, False, out_float32)
+            if M * N * K > self.GENERAL_GEMM_MAX_WORK:
+                if out_float32:
+                    return torch.mm(a, w.t(), out_dtype=torch.float32)
+                return torch.mm(a, w.t())
         out = torch.empty((M, N), dtype=torch.float32 if out_float32 else a.dtype, device=a.device)
         self._check(self.lib.sb_gemm_general(_code(a.dtype), int(out_float32 or a.dtype == torch.float32), _ptr(a), _ptr(w),
                                              _ptr(out), M, N, K, self._stream()), "gemm_general")
         return out
 
     def linear_swiglu(self, h, w_gate_up):
+        """swiglu(h @ w_gate_up^T) for a fused [gate; up] matrix: [M, K] -> [M, rows / 2]."""
+        M, K = h.shape
+        if h.dtype == torch.bfloat16 and K % 8 == 0 and M <= self.SKINNY_MAX_ROWS and w_gate_up.dtype == torch.bfloat16:
+            return self._skinny(h, w_gate_up, w_gate_up.shape[0] // 2, True, False)
         return self.swiglu(self.linear(h, w_gate_up))
 
     # ---- attention ----------------------------------------------------------------------

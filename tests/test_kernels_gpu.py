@@ -73,13 +73,22 @@ def test_swiglu(ops, ref, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("shape", [(1, 389, 96), (5, 70, 33), (130, 257, 160), (64, 1000, 4096), (300, 512, 1024)])
+@pytest.mark.parametrize("shape", [(1, 389, 96), (5, 70, 33), (130, 257, 160), (64, 1000, 4096), (300, 512, 1024),
+                                   (8, 6144, 2560), (16, 2560, 9728), (3, 1000, 4096), (11, 100, 1160)])
 def test_linear(ops, ref, dtype, shape):
     M, N, K = shape
     a, w = rand((M, K), dtype, 6), rand((N, K), dtype, 7, 0.05)
     close(ops.linear(a, w), ref.linear(a, w), dtype, "linear")
     close(ops.linear(a, w, out_float32=True), ref.linear(a, w, out_float32=True), dtype, "linear, 32-bit out",
           rel=2e-5 if dtype == torch.float32 else 2e-3)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("shape", [(1, 2 * 224, 96), (7, 2 * 9728, 2560), (16, 2 * 100, 1160), (40, 2 * 330, 72)])
+def test_linear_swiglu(ops, ref, dtype, shape):
+    M, N2, K = shape
+    h, w = rand((M, K), dtype, 8), rand((N2, K), dtype, 9, 0.05)
+    close(ops.linear_swiglu(h, w), ref.linear_swiglu(h, w), dtype, "linear + swiglu")
 
 
 def make_ctx(cache, ops, slots, q_lens, dtype):
