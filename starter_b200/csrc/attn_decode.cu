@@ -18,7 +18,7 @@
 #include "common.cuh"
 
 #define AD_WARPS 4
-#define AD_STAGES 3
+#define AD_STAGES 2
 #define AD_KEYS_PER_WARP (SB_PAGE / AD_WARPS)  // 16
 
 __device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {

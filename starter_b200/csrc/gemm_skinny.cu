@@ -46,8 +46,10 @@ __device__ __forceinline__ float silu_mul_bf16(float g, float u) {
 
 // NT: activation tiles of 8 rows (M <= 8 * NT).  GATE_UP: W is [2 * n_out, K], gate rows first; warps 0-3
 // take the gate rows of the block, warps 4-7 the matching up rows, and the output is swiglu(gate, up).
-template <int NT, bool GATE_UP>
-__global__ void __launch_bounds__(GS_WARPS * 32)
+// DEEP: a warp requests the next turn's weights before it multiplies the current turn (more bytes in flight
+// per warp, more registers, fewer resident blocks); worth it when few blocks share an SM.
+template <int NT, bool GATE_UP, bool DEEP>
+__global__ void __launch_bounds__(GS_WARPS * 32, DEEP ? 2 : 4)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, void* __restrict__ C,
                    int M, int n_out, int K, int k_per_split, int n_splits, int out_f32, float* __restrict__ partial,
                    int* __restrict__ counters) {
@@ -71,8 +73,9 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     for (int t = 0; t < NT; ++t) acc[t][0] = acc[t][1] = acc[t][2] = acc[t][3] = 0.f;
 
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    for (int kt = k_begin + wk * GS_KWARP; kt < k_end; kt += WPG * GS_KWARP) {
-        uint4 lo[4], hi[4], x[NT][4];
+    // The weights of the next turn are requested before the current turn is multiplied, so that a
+    // warp always has a turn's worth of loads (4 KB) in flight behind the one it works on.
+    auto load_w = [&](uint4 (&lo)[4], uint4 (&hi)[4], int kt) {
 #pragma unroll
         for (int u = 0; u < 4; ++u) {
             const int k = kt + u * 32 + c * 8;
@@ -80,6 +83,9 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
             lo[u] = ok && ok_lo ? load_stream(w_lo + k) : zero;
             hi[u] = ok && ok_hi ? load_stream(w_hi + k) : zero;
         }
+    };
+    auto turn = [&](const uint4 (&lo)[4], const uint4 (&hi)[4], int kt) {
+        uint4 x[NT][4];
 #pragma unroll
         for (int t = 0; t < NT; ++t)
 #pragma unroll
@@ -95,6 +101,27 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
                 mma_bf16_16816(acc[t], lo[u].x, hi[u].x, lo[u].y, hi[u].y, x[t][u].x, x[t][u].y);
                 mma_bf16_16816(acc[t], lo[u].z, hi[u].z, lo[u].w, hi[u].w, x[t][u].z, x[t][u].w);
             }
+    };
+    constexpr int STRIDE = WPG * GS_KWARP;
+    int kt = k_begin + wk * GS_KWARP;
+    if (DEEP) {
+        uint4 lo_a[4], hi_a[4], lo_b[4], hi_b[4];
+        if (kt < k_end) load_w(lo_a, hi_a, kt);
+        while (kt < k_end) {
+            if (kt + STRIDE < k_end) load_w(lo_b, hi_b, kt + STRIDE);
+            turn(lo_a, hi_a, kt);
+            kt += STRIDE;
+            if (kt >= k_end) break;
+            if (kt + STRIDE < k_end) load_w(lo_a, hi_a, kt + STRIDE);
+            turn(lo_b, hi_b, kt);
+            kt += STRIDE;
+        }
+    } else {
+        for (; kt < k_end; kt += STRIDE) {
+            uint4 lo[4], hi[4];
+            load_w(lo, hi, kt);
+            turn(lo, hi, kt);
+        }
     }
 
     // Warps meet: red[warp][weight row][activation row].
@@ -168,7 +195,7 @@ long long sb_gemm_skinny_scratch_floats(int M, int n_out, int n_splits, int gate
 // A [M, K], W [n_out, K] (or [2 * n_out, K] with gate_up), C [M, n_out] bfloat16 or float.
 // Takes M <= 16 and K a multiple of 8; k_per_split a multiple of 128.
 int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int K, int n_splits, int k_per_split,
-                   int gate_up, int out_f32, float* partial, int* counters, cudaStream_t stream) {
+                   int gate_up, int out_f32, int deep, float* partial, int* counters, cudaStream_t stream) {
     if (M <= 0 || n_out <= 0) return 0;
     if (M > 16 || (K & 7) || n_splits < 1 || n_splits > 65535 || (k_per_split % GS_KWARP) ||
         (long long)k_per_split * n_splits < K)
@@ -176,8 +203,15 @@ int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int 
     dim3 grid((n_out + GS_ROWS - 1) / GS_ROWS, n_splits);
     const __nv_bfloat16* a = (const __nv_bfloat16*)A;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
-#define SB_SKINNY(NT, GU) \
-    gemm_skinny_kernel<NT, GU><<<grid, GS_WARPS * 32, 0, stream>>>(a, w, C, M, n_out, K, k_per_split, n_splits, out_f32, partial, counters)
+#define SB_SKINNY(NT, GU)                                                                                              \
+    do {                                                                                                               \
+        if (deep)                                                                                                      \
+            gemm_skinny_kernel<NT, GU, true><<<grid, GS_WARPS * 32, 0, stream>>>(a, w, C, M, n_out, K, k_per_split,      \
+                                                                               n_splits, out_f32, partial, counters); \
+        else                                                                                                           \
+            gemm_skinny_kernel<NT, GU, false><<<grid, GS_WARPS * 32, 0, stream>>>(a, w, C, M, n_out, K, k_per_split,     \
+                                                                                n_splits, out_f32, partial, counters);\
+    } while (0)
     if (M <= 8) {
         if (gate_up) SB_SKINNY(1, true); else SB_SKINNY(1, false);
     } else {

@@ -67,10 +67,10 @@ class Ops:
             "sb_qk_rope_store": [c_int, c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_int, c_void_p, c_void_p,
                                  c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
             "sb_attention_general": [c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_void_p],
-            "sb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p,
-                               c_void_p, c_void_p],
+            "sb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                               c_void_p, c_void_p, c_void_p],
             "sb_attn_decode": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
-            "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p],
+            "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
                           c_void_p],
         }
@@ -80,6 +80,7 @@ class Ops:
             fn.restype = c_int
         self._scratch = {}
         self._sm_count = None
+        self.force_skinny = None  # (K slices, deep) for tuning runs; None = the rules below
 
     # ---- plumbing -----------------------------------------------------------------------
 
@@ -162,13 +163,19 @@ class Ops:
 
     # ---- products -----------------------------------------------------------------------
 
-    SKINNY_MAX_ROWS = 16
+    SKINNY_MAX_ROWS = 8   # up to 16 run, but cuBLAS is faster from 9 rows on
+
+    def skinny_splits(self, blocks: int, K: int) -> int:
+        """K slices per block of 16 weight rows: enough blocks for three per SM, but no slice
+        shorter than 3072 columns (measured on the 4B shapes: short slices cost more in the
+        pass through scratch memory than they gain in parallelism)."""
+        return max(1, min(round(3 * self.sm_count() / blocks), K // 3072))
 
     def _skinny(self, a, w, n_out, gate_up, out_float32):
         """The weight-streaming product for a handful of rows (see gemm_skinny.cu)."""
         M, K = a.shape
         blocks = -(-n_out // 16)
-        want = max(1, min(-(-4 * self.sm_count() // blocks), -(-K // 1024)))
+        want = self.skinny_splits(blocks, K) if self.force_skinny is None else self.force_skinny[0]
         k_per_split = -(-K // want // 128) * 128 if want > 1 else -(-K // 128) * 128
         n_splits = -(-K // k_per_split)
         key = ("gemm_skinny", a.device, M > 8, n_out, n_splits, gate_up)
@@ -179,8 +186,10 @@ class Ops:
                    torch.zeros(blocks, dtype=torch.int32, device=a.device))
             self._scratch[key] = buf
         out = torch.empty((M, n_out), dtype=torch.float32 if out_float32 else torch.bfloat16, device=a.device)
+        deep = False if self.force_skinny is None else self.force_skinny[1]
         self._check(self.lib.sb_gemm_skinny(_ptr(a), _ptr(w), _ptr(out), M, n_out, K, n_splits, k_per_split, int(gate_up),
-                                            int(out_float32), _ptr(buf[0]), _ptr(buf[1]), self._stream()), "gemm_skinny")
+                                            int(out_float32), int(deep), _ptr(buf[0]), _ptr(buf[1]), self._stream()),
+                    "gemm_skinny")
         return out
 
     def linear(self, a, w, out_float32=False):
@@ -240,11 +249,12 @@ class Ops:
             self._sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         return self._sm_count
 
-    def decode_splits(self, n_seqs: int, n_kv_heads: int, max_pages: int) -> int:
-        """How many blocks share one (sequence, kv head): enough to give every SM two blocks.
+    def decode_splits(self, n_seqs: int, n_kv_heads: int, max_pages: int, head_dim: int = 128) -> int:
+        """How many blocks share one (sequence, kv head): as many as keep all blocks resident at once
+        (three per SM at head size 128, by shared memory and registers), so there is no second wave.
         A function of shapes only, so that a captured graph stays valid as sequences grow."""
-        want = -(-2 * self.sm_count() // max(n_seqs * n_kv_heads, 1))
-        return max(1, min(want, max_pages, 64))
+        resident = (3 if head_dim > 64 else 4) * self.sm_count()
+        return max(1, min(resident // max(n_seqs * n_kv_heads, 1), max_pages, 64))
 
     def _decode_scratch(self, device, n_seqs, n_heads, n_kv_heads, head_dim, n_splits):
         key = ("attn_decode", device, n_seqs, n_heads, n_kv_heads, head_dim, n_splits)
@@ -265,7 +275,7 @@ class Ops:
         if (q.dtype == torch.bfloat16 and ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and kv.head_dim in (64, 128)
                 and n_heads // kv.n_kv_heads <= 16):
             g = layer_cache.group
-            n_splits = self.decode_splits(ctx.n_seqs, kv.n_kv_heads, g.table_width)
+            n_splits = self.decode_splits(ctx.n_seqs, kv.n_kv_heads, g.table_width, kv.head_dim)
             partial, counters = self._decode_scratch(q.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, n_splits)
             self._check(self.lib.sb_attn_decode(_ptr(q), _ptr(out), self._batch(ctx), kv, n_heads, scale, int(window or 0),
                                                 n_splits, _ptr(partial), _ptr(counters), self._stream()), "attn_decode")
@@ -277,8 +287,15 @@ class Ops:
     # ---- sampling -----------------------------------------------------------------------
 
     def argmax(self, logits):
-        out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
-        self._check(self.lib.sb_argmax(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], self._stream()), "argmax")
+        rows = logits.shape[0]
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+        key = ("argmax", logits.device, rows)
+        buf = self._scratch.get(key)
+        if buf is None:
+            buf = self._scratch[key] = (torch.empty(rows * 32, dtype=torch.float32, device=logits.device),
+                                        torch.empty(rows * 32, dtype=torch.int32, device=logits.device))
+        self._check(self.lib.sb_argmax(_ptr(logits), _ptr(out), rows, logits.shape[1], _ptr(buf[0]), _ptr(buf[1]),
+                                       self._stream()), "argmax")
         return out
 
     def sample(self, logits, temperature, top_k, seed, request_ids, steps, advance=False):

@@ -54,6 +54,60 @@ __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, c
     }
 }
 
+// bfloat16 rows whose width is a multiple of 8 and at most 8192: every thread holds eight
+// consecutive values, so the row is read once and the whole norm is one pass.
+template <class W, bool ADD>
+__global__ void rmsnorm_vec_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
+                                   const W* __restrict__ weight, __nv_bfloat16* __restrict__ out, int width, float eps) {
+    __shared__ float red[33];
+    const long long base = (long long)blockIdx.x * width;
+    const int c = threadIdx.x * 8;
+    const bool active = c < width;
+    float v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = 0.f;
+    if (active) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(x + base + c);
+        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float2 f = __bfloat1622float2(h[e]);
+            v[2 * e] = f.x;
+            v[2 * e + 1] = f.y;
+        }
+        if (ADD) {
+            const uint4 draw = *reinterpret_cast<const uint4*>(delta + base + c);
+            const __nv_bfloat162* dh = reinterpret_cast<const __nv_bfloat162*>(&draw);
+            uint4 sum;
+            __nv_bfloat162* sh = reinterpret_cast<__nv_bfloat162*>(&sum);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 f = __bfloat1622float2(dh[e]);
+                sh[e] = __floats2bfloat162_rn(__fadd_rn(v[2 * e], f.x), __fadd_rn(v[2 * e + 1], f.y));
+                const float2 back = __bfloat1622float2(sh[e]);
+                v[2 * e] = back.x;
+                v[2 * e + 1] = back.y;
+            }
+            *reinterpret_cast<uint4*>(x + base + c) = sum;
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) ss = fmaf(v[e], v[e], ss);
+    ss = block_sum(ss, red);
+    const float rstd = 1.0f / sqrtf(ss / (float)width + eps);
+    if (active) {
+        uint4 res;
+        __nv_bfloat162* rh = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float n0 = rnd<__nv_bfloat16>(__fmul_rn(v[2 * e], rstd)), n1 = rnd<__nv_bfloat16>(__fmul_rn(v[2 * e + 1], rstd));
+            rh[e] = __floats2bfloat162_rn(__fmul_rn(n0, to_f<W>(weight[c + 2 * e])), __fmul_rn(n1, to_f<W>(weight[c + 2 * e + 1])));
+        }
+        *reinterpret_cast<uint4*>(out + base + c) = res;
+    }
+}
+
 template <class T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
     const long long row = blockIdx.x;
@@ -116,6 +170,19 @@ int sb_rmsnorm(int dtype, int wdtype, void* x, const void* delta, const void* we
     if (dtype == SB_F32) {
         if (wdtype != SB_F32) return (int)cudaErrorInvalidValue;
         SB_NORM(float, float);
+    } else if ((width & 7) == 0 && width <= 8192) {
+        const int vt = ((width / 8 + 31) / 32) * 32;
+#define SB_VNORM(W)                                                                                                  \
+    do {                                                                                                             \
+        if (delta)                                                                                                   \
+            rmsnorm_vec_kernel<W, true><<<rows, vt, 0, stream>>>((__nv_bfloat16*)x, (const __nv_bfloat16*)delta,      \
+                                                                  (const W*)weight, (__nv_bfloat16*)out, width, eps); \
+        else                                                                                                         \
+            rmsnorm_vec_kernel<W, false><<<rows, vt, 0, stream>>>((__nv_bfloat16*)x, nullptr, (const W*)weight,       \
+                                                                   (__nv_bfloat16*)out, width, eps);                 \
+    } while (0)
+        if (wdtype == SB_F32) SB_VNORM(float); else SB_VNORM(__nv_bfloat16);
+#undef SB_VNORM
     } else if (wdtype == SB_F32) {
         SB_NORM(__nv_bfloat16, float);
     } else {

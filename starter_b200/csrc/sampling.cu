@@ -17,21 +17,13 @@ __device__ __forceinline__ unsigned int ordered_key(float v) {
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);  // larger float <=> larger key
 }
 
-__global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab) {
-    __shared__ float best_v[32];
-    __shared__ int best_i[32];
-    const float* row = logits + (long long)blockIdx.x * vocab;
-    float bv = -INFINITY;
-    int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = row[i];
-        if (v > bv || bi == 0x7fffffff) { bv = v; bi = i; }
-    }
+// Best (value, index) of a block; lowest index among equal values.  Result valid in thread 0.
+__device__ __forceinline__ void block_best(float& bv, int& bi, float* best_v, int* best_i) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+        if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
     }
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
     if (lane == 0) { best_v[warp] = bv; best_i[warp] = bi; }
@@ -46,7 +38,31 @@ __global__ void argmax_kernel(const float* __restrict__ logits, int* __restrict_
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
             if (oi != 0x7fffffff && (bi == 0x7fffffff || ov > bv || (ov == bv && oi < bi))) { bv = ov; bi = oi; }
         }
-        if (lane == 0) out[blockIdx.x] = bi;
+    }
+}
+
+// Stage 1: grid (rows, chunks); each block finds the best of its slice of the row.
+// Stage 2 (chunks == 1 or the second launch): one block per row over the stage-1 candidates.
+__global__ void argmax_kernel(const float* __restrict__ values, const int* __restrict__ indices, int n, int row_stride,
+                              float* __restrict__ out_v, int* __restrict__ out_i) {
+    __shared__ float best_v[32];
+    __shared__ int best_i[32];
+    const int chunks = gridDim.y;
+    const int per = (n + chunks - 1) / chunks;
+    const int begin = blockIdx.y * per, end = min(n, begin + per);
+    const float* row = values + (long long)blockIdx.x * row_stride;
+    const int* idx = indices ? indices + (long long)blockIdx.x * row_stride : nullptr;
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = row[i];
+        const int id = idx ? idx[i] : i;
+        if (bi == 0x7fffffff || v > bv || (v == bv && id < bi)) { bv = v; bi = id; }
+    }
+    block_best(bv, bi, best_v, best_i);
+    if (threadIdx.x == 0) {
+        if (out_v) out_v[blockIdx.x * chunks + blockIdx.y] = bv;
+        out_i[blockIdx.x * chunks + blockIdx.y] = bi;
     }
 }
 
@@ -207,9 +223,16 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
 
 extern "C" {
 
-int sb_argmax(const float* logits, int* out, int rows, int vocab, cudaStream_t stream) {
+// scratch_v, scratch_i: rows * SB_ARGMAX_CHUNKS entries each, for the candidates of stage 1.
+int sb_argmax(const float* logits, int* out, int rows, int vocab, float* scratch_v, int* scratch_i, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    argmax_kernel<<<rows, 1024, 0, stream>>>(logits, out, vocab);
+    const int chunks = vocab >= 16384 ? 32 : 1;
+    if (chunks == 1) {
+        argmax_kernel<<<dim3(rows, 1), 1024, 0, stream>>>(logits, nullptr, vocab, vocab, nullptr, out);
+    } else {
+        argmax_kernel<<<dim3(rows, chunks), 512, 0, stream>>>(logits, nullptr, vocab, vocab, scratch_v, scratch_i);
+        argmax_kernel<<<dim3(rows, 1), 32, 0, stream>>>(scratch_v, scratch_i, chunks, chunks, nullptr, out);
+    }
     SB_LAUNCH_CHECK();
 }
 
