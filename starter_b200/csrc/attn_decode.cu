@@ -248,18 +248,48 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
     __syncthreads();
     if (!s_is_last) return;
     __threadfence();
+    // Weights of the splits first (each thread fetches other entries, so the loads overlap), then
+    // the weighted sums with the loads of several splits in flight at once.
+    float* s_w = reinterpret_cast<float*>(pipe);            // [G][n_splits] exp2(m_s - M), then
+    float* s_l = s_w + G * n_splits;                        // [G][n_splits] l_s
+    const float* base = partial + (long long)seq * n_heads * n_splits * part_stride;
+    for (int i = tid; i < G * n_splits; i += AD_WARPS * 32) {
+        const int r = i / n_splits, s = i % n_splits;
+        const float* p = base + ((long long)(kvh * G + r) * n_splits + s) * part_stride;
+        s_w[i] = __ldcg(p + D);
+        s_l[i] = __ldcg(p + D + 1);
+    }
+    __syncthreads();
+    for (int r = warp; r < G; r += AD_WARPS) {
+        float M = -INFINITY;
+        for (int s = lane; s < n_splits; s += 32) M = fmaxf(M, s_w[r * n_splits + s]);
+        M = warp_max(M);
+        for (int s = lane; s < n_splits; s += 32) {
+            const float ms = s_w[r * n_splits + s];
+            s_w[r * n_splits + s] = ms == -INFINITY ? 0.f : exp2f(ms - M);
+        }
+    }
+    __syncthreads();
     for (int i = tid; i < G * D; i += AD_WARPS * 32) {
         const int r = i / D, d = i % D;
         const int head = kvh * G + r;
-        const float* p = partial + ((long long)seq * n_heads + head) * n_splits * part_stride;
-        float M = -INFINITY;
-        for (int s = 0; s < n_splits; ++s) M = fmaxf(M, __ldcg(p + s * part_stride + D));
+        const float* p = base + (long long)head * n_splits * part_stride + d;
+        const float* w = s_w + r * n_splits;
         float o = 0.f, L = 0.f;
-        for (int s = 0; s < n_splits; ++s) {
-            const float ms = __ldcg(p + s * part_stride + D);
-            const float wgt = ms == -INFINITY ? 0.f : exp2f(ms - M);
-            o += __ldcg(p + s * part_stride + d) * wgt;
-            L += __ldcg(p + s * part_stride + D + 1) * wgt;
+        int s = 0;
+        for (; s + 8 <= n_splits; s += 8) {
+            float v[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) v[e] = __ldcg(p + (s + e) * part_stride);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                o += v[e] * w[s + e];
+                L += s_l[r * n_splits + s + e] * w[s + e];
+            }
+        }
+        for (; s < n_splits; ++s) {
+            o += __ldcg(p + s * part_stride) * w[s];
+            L += s_l[r * n_splits + s] * w[s];
         }
         out[((long long)row * n_heads + head) * D + d] = __float2bfloat16_rn(o / L);
     }
