@@ -337,3 +337,65 @@ int sb_attn_decode(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads
 }
 
 }  // extern "C"
+
+// ---------------------------------------------------------------------------------------------
+// The same kernel for callers that cannot allocate: scratch in a fixed device array.
+// Declaration, limits and rules of use: attn_decode_noalloc.h.
+#include <stdio.h>
+
+#include "attn_decode_noalloc.h"
+
+// Counters first (ints), then the partial results (floats).  In host code this name is only a
+// handle for cudaGetSymbolAddress, never a device address.
+static __device__ __align__(256) unsigned char sb_noalloc_scratch[SB_NOALLOC_MAX_COUNTERS * sizeof(int) +
+                                                                  (size_t)SB_NOALLOC_MAX_FLOATS * sizeof(float)];
+
+#define SB_NOALLOC_MAX_DEVICES 64
+static void* sb_noalloc_device_ptr[SB_NOALLOC_MAX_DEVICES];
+static thread_local char sb_noalloc_message[256];
+
+extern "C" {
+
+const char* sb_attn_decode_noalloc_error(void) { return sb_noalloc_message; }
+
+int sb_attn_decode_noalloc(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale, int window,
+                           int n_splits, cudaStream_t stream) {
+    sb_noalloc_message[0] = 0;
+    if (batch.n_seqs <= 0) return 0;
+    const long long counters_needed = (long long)batch.n_seqs * kv.n_kv_heads;
+    const long long floats_needed = sb_attn_decode_scratch_floats(batch.n_seqs, n_heads, kv.head_dim, n_splits);
+    if (counters_needed > SB_NOALLOC_MAX_COUNTERS || floats_needed > SB_NOALLOC_MAX_FLOATS) {
+        snprintf(sb_noalloc_message, sizeof(sb_noalloc_message),
+                 "sb_attn_decode_noalloc: the call needs %lld counters and %lld floats of scratch; the fixed array "
+                 "holds %d and %d (use sb_attn_decode with scratch of your own, or fewer splits)",
+                 counters_needed, floats_needed, SB_NOALLOC_MAX_COUNTERS, SB_NOALLOC_MAX_FLOATS);
+        return SB_NOALLOC_TOO_LARGE;
+    }
+    int device = -1;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= SB_NOALLOC_MAX_DEVICES) {
+        snprintf(sb_noalloc_message, sizeof(sb_noalloc_message), "sb_attn_decode_noalloc: device %d is beyond the %d this "
+                 "entry point keeps addresses for", device, SB_NOALLOC_MAX_DEVICES);
+        return SB_NOALLOC_SETUP_FAILED;
+    }
+    if (sb_noalloc_device_ptr[device] == nullptr) {
+        // Set-up, once per device, with that device current: the array's address on this device.
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, sb_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            snprintf(sb_noalloc_message, sizeof(sb_noalloc_message), "sb_attn_decode_noalloc: cudaGetSymbolAddress failed: %s",
+                     cudaGetErrorString(e));
+            return e != cudaSuccess ? (int)e : SB_NOALLOC_SETUP_FAILED;
+        }
+        sb_noalloc_device_ptr[device] = p;
+    }
+    int* counters = reinterpret_cast<int*>(sb_noalloc_device_ptr[device]);
+    float* partial = reinterpret_cast<float*>(counters + SB_NOALLOC_MAX_COUNTERS);
+    // The array keeps the last call's contents: the counters must start at zero.
+    e = cudaMemsetAsync(counters, 0, counters_needed * sizeof(int), stream);
+    if (e != cudaSuccess) return (int)e;
+    return sb_attn_decode(q, out, batch, kv, n_heads, scale, window, n_splits, partial, counters, stream);
+}
+
+}  // extern "C"

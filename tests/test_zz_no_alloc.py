@@ -1,0 +1,85 @@
+"""The decode-attention entry point that allocates nothing, called through its exported C symbol.
+
+Some callers of the kernels cannot allocate device memory (they run inside another framework's
+memory plan, or are handed their buffers and nothing else).  For them the library exports
+``sb_attn_decode_noalloc``: the split-key decode attention with its scratch in a fixed array
+inside the library instead of in buffers the caller allocates.  This test calls that symbol
+with ctypes, twice in a row on different inputs, and compares each result with the ordinary
+entry point ``sb_attn_decode`` given scratch from torch; it also checks that a call too large
+for the fixed array is refused with a message.  The file's name makes pytest collect it last.
+"""
+
+import ctypes
+import math
+from ctypes import c_float, c_int, c_void_p
+
+import pytest
+import torch
+
+from starter_b200.cache import Cache, KVRequest
+
+pytestmark = pytest.mark.gpu
+
+
+def _setup(heads, kv_heads, head_dim, lengths, seed):
+    from starter_b200.csrc.ops import SbBatch, SbKV
+    dtype = torch.bfloat16
+    cache = Cache([KVRequest(kv_heads, head_dim)], n_slots=len(lengths), max_tokens=64 * 40, dtype=dtype, device="cuda",
+                  max_seq_tokens=1024)
+    g = torch.Generator().manual_seed(seed)
+    group = cache.groups[0]
+    group.k.copy_(torch.randn(group.k.shape, generator=g).to(dtype))
+    group.v.copy_(torch.randn(group.v.shape, generator=g).to(dtype))
+    slots = [cache.alloc() for _ in lengths]
+    for s, n in zip(slots, lengths):
+        cache.assume_length(s, n)
+        cache.reserve(s, n + 1)
+    cache.flush()
+    n = len(lengths)
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    keep = dict(seq_slot=i32(slots), cu_q=i32(list(range(n + 1))), row_seq=i32(list(range(n))), cache=cache)
+    batch = SbBatch(keep["seq_slot"].data_ptr(), keep["cu_q"].data_ptr(), keep["row_seq"].data_ptr(),
+                    cache.lengths.data_ptr(), n, n, cache.null_slot, 0)
+    kv = SbKV(group.k[0].data_ptr(), group.v[0].data_ptr(), group.table.data_ptr(), group.table_width, 0, kv_heads, head_dim)
+    q = torch.randn(n, heads * head_dim, generator=g).to(dtype).cuda()
+    return keep, batch, kv, q
+
+
+def test_no_alloc_entry_point_matches_the_ordinary_one():
+    from starter_b200.csrc.build import load
+    from starter_b200.csrc.ops import SbBatch, SbKV
+    lib = load(verbose=False)
+    ordinary = lib.sb_attn_decode
+    ordinary.argtypes = [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p]
+    ordinary.restype = c_int
+    noalloc = lib.sb_attn_decode_noalloc
+    noalloc.argtypes = [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p]
+    noalloc.restype = c_int
+    message = lib.sb_attn_decode_noalloc_error
+    message.restype = ctypes.c_char_p
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    # two calls in a row, with different shapes and split counts, each against the ordinary entry point
+    for heads, kv_heads, head_dim, lengths, n_splits, seed in [(8, 2, 128, [700, 5, 64, 300], 5, 1),
+                                                               (4, 4, 64, [1000, 0, 129], 3, 2)]:
+        keep, batch, kv, q = _setup(heads, kv_heads, head_dim, lengths, seed)
+        n = len(lengths)
+        scale = 1.0 / math.sqrt(head_dim)
+        partial = torch.empty(n * heads * n_splits * (head_dim + 2), dtype=torch.float32, device="cuda")
+        counters = torch.zeros(n * kv_heads, dtype=torch.int32, device="cuda")
+        want = torch.empty_like(q)
+        assert ordinary(q.data_ptr(), want.data_ptr(), batch, kv, heads, scale, 0, n_splits, partial.data_ptr(),
+                        counters.data_ptr(), stream) == 0
+        got = torch.full_like(q, float("nan"))
+        code = noalloc(q.data_ptr(), got.data_ptr(), batch, kv, heads, scale, 0, n_splits, stream)
+        assert code == 0, message().decode()
+        torch.cuda.synchronize()
+        scale_ref = float(want.float().abs().max())
+        assert float((got.float() - want.float()).abs().max()) <= 1.6e-2 * scale_ref
+        assert torch.isfinite(got.float()).all()
+
+    # a call that needs more scratch than the fixed array holds is refused, with a message
+    keep, batch, kv, q = _setup(8, 2, 128, [10] * 40, 3)
+    big = SbBatch(batch.seq_slot, batch.cu_q, batch.row_seq, batch.lengths, 4000, 4000, batch.null_slot, 0)
+    code = noalloc(q.data_ptr(), q.data_ptr(), big, kv, 8, 1.0, 0, 64, stream)
+    assert code == -1 and b"scratch" in message()
