@@ -16,43 +16,11 @@
 // sequence grows.  With more than one split each block leaves its partial result in scratch
 // memory and the last one to arrive (an atomic counter per sequence and kv head) merges them.
 #include "common.cuh"
+#include "mma_utils.cuh"
 
 #define AD_WARPS 4
 #define AD_STAGES 2
 #define AD_KEYS_PER_WARP (SB_PAGE / AD_WARPS)  // 16
-
-__device__ __forceinline__ void cp_async_16(void* smem_dst, const void* gmem_src) {
-    const unsigned int s = (unsigned int)__cvta_generic_to_shared(smem_dst);
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;\n" ::"r"(s), "l"(gmem_src));
-}
-__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;\n" ::); }
-template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;\n" ::"n"(N)); }
-
-__device__ __forceinline__ void ldmatrix_x4(unsigned int (&r)[4], const void* smem_ptr) {
-    const unsigned int s = (unsigned int)__cvta_generic_to_shared(smem_ptr);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void ldmatrix_x4_trans(unsigned int (&r)[4], const void* smem_ptr) {
-    const unsigned int s = (unsigned int)__cvta_generic_to_shared(smem_ptr);
-    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(s));
-}
-__device__ __forceinline__ void mma_bf16(float (&c)[4], const unsigned int (&a)[4], unsigned int b0, unsigned int b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ unsigned int pack_bf16(float lo, float hi) {
-    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
-    return *reinterpret_cast<unsigned int*>(&v);
-}
-
-// Byte offset of 16-byte chunk `chunk` of row `row` in a [rows][D] bfloat16 tile whose chunks
-// are XOR-swizzled by the row so that ldmatrix reads eight rows without bank conflicts.
-template <int D> __device__ __forceinline__ int tile_off(int row, int chunk) {
-    return row * (D * 2) + ((chunk ^ (row & 7)) << 4);
-}
 
 template <int D>
 __global__ void __launch_bounds__(AD_WARPS * 32)

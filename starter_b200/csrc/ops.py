@@ -69,6 +69,7 @@ class Ops:
             "sb_attention_general": [c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_void_p],
             "sb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_void_p, c_void_p, c_void_p],
+            "sb_attn_prefill": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p],
             "sb_attn_decode": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
@@ -267,18 +268,22 @@ class Ops:
         return buf
 
     def attention(self, ctx, q, layer_cache, n_heads, scale, window):
-        """Causal attention of the step's rows over the layer's cache.  Steps of one token per
-        sequence in bfloat16 with head size 64 or 128 take the split-key decode kernel; everything
-        else takes the general kernel."""
+        """Causal attention of the step's rows over the layer's cache.  bfloat16 with head size 64 or
+        128: the split-key decode kernel for steps of one token per sequence, the flash kernel for
+        everything else.  Other head sizes and float32 take the general kernel."""
         out = torch.empty_like(q)
         kv = self._kv(layer_cache)
-        if (q.dtype == torch.bfloat16 and ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and kv.head_dim in (64, 128)
-                and n_heads // kv.n_kv_heads <= 16):
-            g = layer_cache.group
-            n_splits = self.decode_splits(ctx.n_seqs, kv.n_kv_heads, g.table_width, kv.head_dim)
-            partial, counters = self._decode_scratch(q.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, n_splits)
-            self._check(self.lib.sb_attn_decode(_ptr(q), _ptr(out), self._batch(ctx), kv, n_heads, scale, int(window or 0),
-                                                n_splits, _ptr(partial), _ptr(counters), self._stream()), "attn_decode")
+        if q.dtype == torch.bfloat16 and kv.head_dim in (64, 128):
+            if ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and n_heads // kv.n_kv_heads <= 16:
+                g = layer_cache.group
+                n_splits = self.decode_splits(ctx.n_seqs, kv.n_kv_heads, g.table_width, kv.head_dim)
+                partial, counters = self._decode_scratch(q.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, n_splits)
+                self._check(self.lib.sb_attn_decode(_ptr(q), _ptr(out), self._batch(ctx), kv, n_heads, scale,
+                                                    int(window or 0), n_splits, _ptr(partial), _ptr(counters),
+                                                    self._stream()), "attn_decode")
+            else:
+                self._check(self.lib.sb_attn_prefill(_ptr(q), _ptr(out), self._batch(ctx), kv, n_heads, scale,
+                                                     int(window or 0), ctx.max_q_len, self._stream()), "attn_prefill")
             return out
         self._check(self.lib.sb_attention_general(_code(q.dtype), _ptr(q), _ptr(out), self._batch(ctx), kv,
                                                   n_heads, scale, int(window or 0), self._stream()), "attention_general")

@@ -106,7 +106,9 @@ def make_ctx(cache, ops, slots, q_lens, dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(6, 3, 48, None), (4, 1, 16, 9), (8, 8, 128, None), (2, 2, 80, 70)])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(6, 3, 48, None), (4, 1, 16, 9), (8, 8, 128, None), (2, 2, 80, 70),
+                                                            (8, 2, 128, None), (6, 1, 64, None), (4, 2, 64, 40),
+                                                            (20, 1, 128, 90)])
 def test_store_and_attention(ops, ref, dtype, heads, kv_heads, head_dim, window):
     """Two steps over three sequences of unequal length: rope + store + attention against the
     torch restatement working on a second, identical cache."""
@@ -241,3 +243,36 @@ def test_skinny_product_variants(ops, ref, M, splits, deep):
         close(ops._skinny(a, w, 1000, True, False), ref.linear_swiglu(a, w), dtype, "skinny + swiglu")
     finally:
         ops.force_skinny = None
+
+
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(8, 2, 128, None), (3, 1, 64, 150)])
+def test_prefill_attention_over_many_pages(ops, ref, heads, kv_heads, head_dim, window):
+    """Long pieces appended to contexts that already hold tokens; one far key is made to stand out."""
+    dtype = torch.bfloat16
+    caches = [Cache([KVRequest(kv_heads, head_dim, window)], n_slots=3, max_tokens=64 * 40, dtype=dtype, device="cuda",
+                    max_step_tokens=512) for _ in range(2)]
+    for step, q_lens in enumerate([(200, 64), (450, 333)]):
+        outs = []
+        qkv = rand((sum(q_lens), (heads + 2 * kv_heads) * head_dim), dtype, 80 + step, 0.5)
+        if step == 0:
+            qkv[37, heads * head_dim:(heads + 1) * head_dim] = 3.0     # key 37 of sequence 0 is large ...
+        elif window is None:
+            qkv[449, :head_dim] = 3.0                                  # ... and a late query of head 0 points at it
+        for c, o in zip(caches, (ops, ref)):
+            sl = [0, 1]
+            if step == 0:
+                assert [c.alloc(), c.alloc()] == sl
+            for s_, n in zip(sl, q_lens):
+                c.reserve(s_, c.lengths_host[s_] + n)
+            c.flush()
+            ctx = make_ctx(c, ops, sl, q_lens, dtype)
+            q = o.qk_norm_rope_store(ctx, qkv, c.layers[0], heads, kv_heads, head_dim, None, None, 0.0, None)
+            outs.append(o.attention(ctx, q, c.layers[0], heads, 1.0 / math.sqrt(head_dim), window))
+            o.advance_lengths(ctx)
+            for s_, n in zip(sl, q_lens):
+                c.advance_host(s_, n)
+        close(outs[0], outs[1], dtype, f"prefill attention, step {step}")
+    if window is None:
+        want = caches[0].groups[0].v[0, int(caches[0].groups[0].table_host[0, 0]), 0, 37].float()
+        got = outs[0][449, :head_dim].float()
+        assert float((got - want).abs().max()) < 0.05 * float(want.abs().max())
