@@ -51,7 +51,8 @@ class StateRequest:
 
 @dataclass(frozen=True)
 class SharedRequest:
-    """A mixer that reads the cache of layer ``layer`` and stores nothing itself."""
+    """A mixer that reads the cache of another layer and stores nothing itself.  In a mixer's answer
+    ``layer`` is a layer index; in the list a Cache is built from, it is an index into that list."""
 
     layer: int
 
@@ -165,8 +166,8 @@ class LayerCache:
 class Cache:
     """Slots, lengths, and the groups' storage for one model.
 
-    ``requests[i]`` is what layer i's mixer asked for (a KVRequest, StateRequest,
-    SharedRequest or None).  ``max_tokens`` bounds the tokens all live sequences
+    ``requests[i]`` is what the i-th entry of the model's execution order asked for (a
+    KVRequest, StateRequest, SharedRequest naming an earlier entry, or None).  ``max_tokens`` bounds the tokens all live sequences
     hold together, each sequence's count rounded up to ``PAGE``; ``max_seq_tokens``
     bounds one sequence; ``max_step_tokens`` bounds the tokens one sequence
     brings in one forward pass (it sizes the ring of a window group).

@@ -79,7 +79,8 @@ class ModelSpec:
     """A decoder: embedding, layers, the order they run in, final norm, output head.
 
     ``schedule`` lists layer indices in execution order; an index may appear
-    more than once (the layer then runs again with the same weights and cache).
+    more than once: the layer then runs again with the same weights, and each occurrence keeps
+    a cache entry of its own.
     """
 
     hidden_size: int

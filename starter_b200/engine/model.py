@@ -73,7 +73,21 @@ class DecoderModel:
     # ---- cache -------------------------------------------------------------------------
 
     def cache_requests(self) -> List[object]:
-        return [block.cache_request() for block in self.blocks]
+        """What each entry of the execution order asks of the cache.  A layer that is named twice runs
+        with the same weights but keeps a cache entry per occurrence (otherwise the second run would
+        overwrite what the first run of a later step has to read).  A mixer that reads another layer's
+        cache gets the entry of that layer's latest earlier occurrence."""
+        from ..cache.cache import SharedRequest
+        requests = []
+        for pos, i in enumerate(self.order):
+            req = self.blocks[i].cache_request()
+            if isinstance(req, SharedRequest):
+                earlier = [p for p in range(pos) if self.order[p] == req.layer]
+                if not earlier:
+                    raise ValueError(f"layer {i} reads the cache of layer {req.layer}, which has not run before it")
+                req = SharedRequest(earlier[-1])
+            requests.append(req)
+        return requests
 
     def prepare(self, cache) -> None:
         """Size position tables and workspaces for the cache the model will run on."""
@@ -85,8 +99,8 @@ class DecoderModel:
     def hidden(self, ctx: StepContext, tokens: torch.Tensor) -> ResidualStream:
         """Run the step's rows through every layer; returns the residual stream before the final norm."""
         stream = ResidualStream(ctx.ops.embed(tokens, self.embedding, ctx.status))
-        for i in self.order:
-            self.blocks[i].forward(ctx, stream, ctx.cache.layers[i])
+        for pos, i in enumerate(self.order):
+            self.blocks[i].forward(ctx, stream, ctx.cache.layers[pos])
         return stream
 
     def logits(self, ctx: StepContext, stream: ResidualStream, rows: Optional[torch.Tensor]) -> torch.Tensor:
