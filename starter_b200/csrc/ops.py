@@ -69,6 +69,9 @@ class Ops:
             "sb_attention_general": [c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_void_p],
             "sb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_void_p, c_void_p, c_void_p],
+            "sb_gemm_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
+                               c_void_p, c_void_p],
+            "sb_gemm_stream_plan": [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int)],
             "sb_attn_prefill": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p],
             "sb_attn_decode": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -82,6 +85,8 @@ class Ops:
         self._scratch = {}
         self._sm_count = None
         self.force_skinny = None  # (K slices, deep) for tuning runs; None = the rules below
+        self.use_stream = True    # the TMA + tcgen05 weight-streaming product for decode-sized rows
+        self._kernel_status = None
 
     # ---- plumbing -----------------------------------------------------------------------
 
@@ -165,6 +170,46 @@ class Ops:
     # ---- products -----------------------------------------------------------------------
 
     SKINNY_MAX_ROWS = 8   # up to 16 run, but cuBLAS is faster from 9 rows on
+    STREAM_MAX_ROWS = 64
+    STREAM_MIN_WORK = 1 << 22   # rows of W times K below which the simpler kernels do as well
+
+    def kernel_status(self, device) -> torch.Tensor:
+        """A status word of the kernels that are not tied to a step (bit 4: a wait inside a kernel timed out)."""
+        if self._kernel_status is None:
+            self._kernel_status = torch.zeros(1, dtype=torch.int32, device=device)
+        return self._kernel_status
+
+    def read_kernel_status(self) -> int:
+        if self._kernel_status is None:
+            return 0
+        bits = int(self._kernel_status.item())
+        if bits:
+            self._kernel_status.zero_()
+        return bits
+
+    def _stream(self, a, w, n_out, gate_up, out_float32):
+        """The TMA + tcgen05 weight-streaming product (see gemm_stream.cu)."""
+        M, K = a.shape
+        key = ("gemm_stream", a.device, n_out, K, gate_up, M <= 16, M <= 32)
+        plan = self._scratch.get(key)
+        if plan is None:
+            grid, tiles, parts = c_int(), c_int(), c_int()
+            self.lib.sb_gemm_stream_plan(n_out, K, self.sm_count(), ctypes.byref(grid), ctypes.byref(tiles), ctypes.byref(parts))
+            bn = 16 if M <= 16 else (32 if M <= 32 else 64)
+            floats = tiles.value * parts.value * bn * (2 if gate_up else 1) * 128
+            plan = (grid.value, parts.value, torch.empty(floats, dtype=torch.float32, device=a.device),
+                    torch.zeros(tiles.value, dtype=torch.int32, device=a.device))
+            self._scratch[key] = plan
+        grid, parts, partial, counters = plan
+        out = torch.empty((M, n_out), dtype=torch.float32 if out_float32 else torch.bfloat16, device=a.device)
+        self._check(self.lib.sb_gemm_stream(_ptr(a), _ptr(w), _ptr(out), M, n_out, K, int(gate_up), int(out_float32), grid,
+                                            parts, _ptr(partial), _ptr(counters), _ptr(self.kernel_status(a.device)),
+                                            self._stream()), "gemm_stream")
+        return out
+
+    def _takes_stream(self, M, n_out, K, gate_up) -> bool:
+        return (self.use_stream and M <= (32 if gate_up else self.STREAM_MAX_ROWS) and K % 8 == 0 and K >= 64
+                and n_out * K >= self.STREAM_MIN_WORK)
 
     def skinny_splits(self, blocks: int, K: int) -> int:
         """K slices per block of 16 weight rows: enough blocks for three per SM, but no slice
@@ -203,6 +248,8 @@ class Ops:
         if w.shape[1] != K or a.dtype != w.dtype:
             raise KernelError(f"linear: a is {tuple(a.shape)} {a.dtype}, w is {tuple(w.shape)} {w.dtype}")
         if a.dtype == torch.bfloat16 and K % 8 == 0:
+            if self._takes_stream(M, N, K, False):
+                return self._stream(a, w, N, False, out_float32)
             if M <= self.SKINNY_MAX_ROWS:
                 return self._skinny(a, w, N, False, out_float32)
             if M * N * K > self.GENERAL_GEMM_MAX_WORK:
@@ -217,8 +264,11 @@ class Ops:
     def linear_swiglu(self, h, w_gate_up):
         """swiglu(h @ w_gate_up^T) for a fused [gate; up] matrix: [M, K] -> [M, rows / 2]."""
         M, K = h.shape
-        if h.dtype == torch.bfloat16 and K % 8 == 0 and M <= self.SKINNY_MAX_ROWS and w_gate_up.dtype == torch.bfloat16:
-            return self._skinny(h, w_gate_up, w_gate_up.shape[0] // 2, True, False)
+        if h.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and K % 8 == 0:
+            if self._takes_stream(M, w_gate_up.shape[0] // 2, K, True):
+                return self._stream(h, w_gate_up, w_gate_up.shape[0] // 2, True, False)
+            if M <= self.SKINNY_MAX_ROWS:
+                return self._skinny(h, w_gate_up, w_gate_up.shape[0] // 2, True, False)
         return self.swiglu(self.linear(h, w_gate_up))
 
     # ---- attention ----------------------------------------------------------------------

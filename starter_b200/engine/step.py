@@ -22,9 +22,11 @@ from .context import StepContext
 
 STATUS_BAD_TOKEN = 1
 STATUS_NO_PAGE = 2
+STATUS_TIMEOUT = 4
 STATUS_MESSAGES = {
     STATUS_BAD_TOKEN: "a token id is outside the vocabulary",
     STATUS_NO_PAGE: "a row had no cache page reserved for its position",
+    STATUS_TIMEOUT: "a wait inside a kernel ran out of time; the step's results are not valid",
 }
 
 
@@ -162,5 +164,9 @@ class Stepper:
         bits = int(self.status.item())
         if bits:
             self.status.zero_()
+        read = getattr(self.runtime.ops, "read_kernel_status", None)
+        if read is not None:
+            bits |= read()
+        if bits:
             what = [msg for bit, msg in STATUS_MESSAGES.items() if bits & bit] or [f"status {bits}"]
             raise StepError("; ".join(what))

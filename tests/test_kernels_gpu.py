@@ -276,3 +276,25 @@ def test_prefill_attention_over_many_pages(ops, ref, heads, kv_heads, head_dim, 
         want = caches[0].groups[0].v[0, int(caches[0].groups[0].table_host[0, 0]), 0, 37].float()
         got = outs[0][449, :head_dim].float()
         assert float((got - want).abs().max()) < 0.05 * float(want.abs().max())
+
+
+@pytest.mark.parametrize("shape", [(1, 6144, 2560), (8, 2560, 9728), (16, 1000, 4104), (33, 2560, 4096), (20, 700, 520),
+                                   (64, 151936, 256), (5, 130, 72)])
+def test_stream_product(ops, ref, shape):
+    """The TMA + tcgen05 weight-streaming product: tiles split between blocks, ragged edges in every dimension."""
+    M, N, K = shape
+    dtype = torch.bfloat16
+    a, w = rand((M, K), dtype, 90), rand((N, K), dtype, 91, 0.05)
+    close(ops._stream(a, w, N, False, False), ref.linear(a, w), dtype, "stream")
+    close(ops._stream(a, w, N, False, True), ref.linear(a, w, out_float32=True), dtype, "stream, 32-bit out", rel=2e-3)
+    assert ops.read_kernel_status() == 0
+
+
+@pytest.mark.parametrize("shape", [(8, 9728, 2560), (30, 1000, 1160), (1, 200, 64)])
+def test_stream_product_with_swiglu(ops, ref, shape):
+    M, I, K = shape
+    dtype = torch.bfloat16
+    h, w = rand((M, K), dtype, 92), rand((2 * I, K), dtype, 93, 0.05)
+    close(ops._stream(h, w, I, True, False), ref.linear_swiglu(h, w), dtype, "stream + swiglu")
+    close(ops._stream(h, w, I, True, False), ref.linear_swiglu(h, w), dtype, "stream + swiglu, again")  # counters were left zero
+    assert ops.read_kernel_status() == 0
