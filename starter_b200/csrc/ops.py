@@ -187,7 +187,7 @@ class Ops:
             self._kernel_status.zero_()
         return bits
 
-    def _stream(self, a, w, n_out, gate_up, out_float32):
+    def _stream_product(self, a, w, n_out, gate_up, out_float32):
         """The TMA + tcgen05 weight-streaming product (see gemm_stream.cu)."""
         M, K = a.shape
         key = ("gemm_stream", a.device, n_out, K, gate_up, M <= 16, M <= 32)
@@ -249,7 +249,7 @@ class Ops:
             raise KernelError(f"linear: a is {tuple(a.shape)} {a.dtype}, w is {tuple(w.shape)} {w.dtype}")
         if a.dtype == torch.bfloat16 and K % 8 == 0:
             if self._takes_stream(M, N, K, False):
-                return self._stream(a, w, N, False, out_float32)
+                return self._stream_product(a, w, N, False, out_float32)
             if M <= self.SKINNY_MAX_ROWS:
                 return self._skinny(a, w, N, False, out_float32)
             if M * N * K > self.GENERAL_GEMM_MAX_WORK:
@@ -266,7 +266,7 @@ class Ops:
         M, K = h.shape
         if h.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and K % 8 == 0:
             if self._takes_stream(M, w_gate_up.shape[0] // 2, K, True):
-                return self._stream(h, w_gate_up, w_gate_up.shape[0] // 2, True, False)
+                return self._stream_product(h, w_gate_up, w_gate_up.shape[0] // 2, True, False)
             if M <= self.SKINNY_MAX_ROWS:
                 return self._skinny(h, w_gate_up, w_gate_up.shape[0] // 2, True, False)
         return self.swiglu(self.linear(h, w_gate_up))

@@ -285,8 +285,8 @@ def test_stream_product(ops, ref, shape):
     M, N, K = shape
     dtype = torch.bfloat16
     a, w = rand((M, K), dtype, 90), rand((N, K), dtype, 91, 0.05)
-    close(ops._stream(a, w, N, False, False), ref.linear(a, w), dtype, "stream")
-    close(ops._stream(a, w, N, False, True), ref.linear(a, w, out_float32=True), dtype, "stream, 32-bit out", rel=2e-3)
+    close(ops._stream_product(a, w, N, False, False), ref.linear(a, w), dtype, "stream")
+    close(ops._stream_product(a, w, N, False, True), ref.linear(a, w, out_float32=True), dtype, "stream, 32-bit out", rel=2e-3)
     assert ops.read_kernel_status() == 0
 
 
@@ -295,6 +295,6 @@ def test_stream_product_with_swiglu(ops, ref, shape):
     M, I, K = shape
     dtype = torch.bfloat16
     h, w = rand((M, K), dtype, 92), rand((2 * I, K), dtype, 93, 0.05)
-    close(ops._stream(h, w, I, True, False), ref.linear_swiglu(h, w), dtype, "stream + swiglu")
-    close(ops._stream(h, w, I, True, False), ref.linear_swiglu(h, w), dtype, "stream + swiglu, again")  # counters were left zero
+    close(ops._stream_product(h, w, I, True, False), ref.linear_swiglu(h, w), dtype, "stream + swiglu")
+    close(ops._stream_product(h, w, I, True, False), ref.linear_swiglu(h, w), dtype, "stream + swiglu, again")  # counters were left zero
     assert ops.read_kernel_status() == 0
