@@ -125,7 +125,7 @@ __device__ __forceinline__ float silu_mul_rounded(float g, float u) {
 
 struct StreamArgs {
     void* C;             // [M, n_out] bfloat16 or float
-    float* partial;      // scratch: [tile][max_parts][acc_cols][128] floats
+    float* partial;      // scratch: [tile][max_parts][128][acc_cols] floats
     int* counters;       // one per tile, zero before the first launch; the kernel leaves them zero
     int* status;
     int M, n_out, K;
@@ -265,10 +265,12 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 first_block = block_of_unit((long long)tile * args.k_blocks, U, P);
                 parts = block_of_unit((long long)tile * args.k_blocks + args.k_blocks - 1, U, P) - first_block + 1;
             }
+            // Partial sums of a tile: [tile][part][row][column], a thread's columns side by side.
             float* my_part = args.partial +
-                (((long long)tile * args.max_parts + (blockIdx.x - first_block)) * ACC_COLS) * ST_BM + row_in_tile;
+                (((long long)tile * args.max_parts + (blockIdx.x - first_block)) * ST_BM + row_in_tile) * ACC_COLS;
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 16) {
+                if (c0 >= args.M) break;   // columns beyond the activation rows hold zeros nobody reads
                 float g[16], up[16];
                 tc_ld16(taddr + c0, g);
                 if (GATE_UP) tc_ld16(taddr + BN + c0, up);
@@ -285,9 +287,11 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     }
                 } else {
 #pragma unroll
-                    for (int j = 0; j < 16; ++j) {
-                        my_part[(long long)(c0 + j) * ST_BM] = g[j];
-                        if (GATE_UP) my_part[(long long)(BN + c0 + j) * ST_BM] = up[j];
+                    for (int j = 0; j < 16; j += 4) {
+                        if (c0 + j >= args.M) break;
+                        *reinterpret_cast<float4*>(my_part + c0 + j) = make_float4(g[j], g[j + 1], g[j + 2], g[j + 3]);
+                        if (GATE_UP)
+                            *reinterpret_cast<float4*>(my_part + BN + c0 + j) = make_float4(up[j], up[j + 1], up[j + 2], up[j + 3]);
                     }
                 }
             }
@@ -295,7 +299,8 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);   // the MMA thread may reuse this accumulator
             if (!whole) {
-                // The last block to finish its share of this tile adds the shares up.
+                // The last block to finish its share of this tile adds the shares up, in the order of the
+                // blocks, so the sum does not depend on who came last.
                 __threadfence();
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 if (threadIdx.x == 64) *last_flag = atomicAdd(&args.counters[tile], 1) == parts - 1;
@@ -303,18 +308,45 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                 const bool last = *last_flag != 0;
                 if (last) {
                     __threadfence();
-                    const float* base = args.partial + ((long long)tile * args.max_parts * ACC_COLS) * ST_BM + row_in_tile;
-                    for (int m = 0; m < BN && m < args.M; ++m) {
-                        float gs = 0.f, us = 0.f;
-                        for (int p = 0; p < parts; ++p) {
-                            gs += __ldcg(base + ((long long)p * ACC_COLS + m) * ST_BM);
-                            if (GATE_UP) us += __ldcg(base + ((long long)p * ACC_COLS + BN + m) * ST_BM);
+                    const float* base = args.partial + (((long long)tile * args.max_parts) * ST_BM + row_in_tile) * ACC_COLS;
+                    const long long part_stride = (long long)ST_BM * ACC_COLS;
+                    for (int c0 = 0; c0 < BN && c0 < args.M; c0 += 8) {
+                        float gs[8], us[8];
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) gs[j] = us[j] = 0.f;
+                        for (int p0 = 0; p0 < parts; p0 += 4) {     // four shares' loads in flight at a time
+                            float4 tg[4][2], tu[4][2];
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    const bool on = p0 + q < parts && c0 + 4 * h < args.M;
+                                    const float* src = base + (p0 + q) * part_stride + c0 + 4 * h;
+                                    tg[q][h] = on ? __ldcg(reinterpret_cast<const float4*>(src)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                    if (GATE_UP)
+                                        tu[q][h] = on ? __ldcg(reinterpret_cast<const float4*>(src + BN)) : make_float4(0.f, 0.f, 0.f, 0.f);
+                                }
+#pragma unroll
+                            for (int q = 0; q < 4; ++q)
+#pragma unroll
+                                for (int h = 0; h < 2; ++h) {
+                                    gs[4 * h] += tg[q][h].x; gs[4 * h + 1] += tg[q][h].y;
+                                    gs[4 * h + 2] += tg[q][h].z; gs[4 * h + 3] += tg[q][h].w;
+                                    if (GATE_UP) {
+                                        us[4 * h] += tu[q][h].x; us[4 * h + 1] += tu[q][h].y;
+                                        us[4 * h + 2] += tu[q][h].z; us[4 * h + 3] += tu[q][h].w;
+                                    }
+                                }
                         }
-                        if (n_row < args.n_out) {
-                            const float v = GATE_UP ? silu_mul_rounded(gs, us) : gs;
-                            const long long o = (long long)m * args.n_out + n_row;
-                            if (args.out_f32) ((float*)args.C)[o] = v;
-                            else ((__nv_bfloat16*)args.C)[o] = __float2bfloat16_rn(v);
+#pragma unroll
+                        for (int j = 0; j < 8; ++j) {
+                            const int m = c0 + j;
+                            if (m < args.M && n_row < args.n_out) {
+                                const float v = GATE_UP ? silu_mul_rounded(gs[j], us[j]) : gs[j];
+                                const long long o = (long long)m * args.n_out + n_row;
+                                if (args.out_f32) ((float*)args.C)[o] = v;
+                                else ((__nv_bfloat16*)args.C)[o] = __float2bfloat16_rn(v);
+                            }
                         }
                     }
                     if (threadIdx.x == 64) args.counters[tile] = 0;

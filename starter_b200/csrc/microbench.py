@@ -1,0 +1,111 @@
+"""Times one kernel on one of the decode shapes: replay of a CUDA graph that walks through copies of the
+weights (more bytes than L2 holds), median of several replays.  The reference times its candidate
+kernels the same way (engine/kernels/gemm.py:477-513).
+
+    python -m starter_b200.csrc.microbench --kernel stream --shape gateup --rows 8
+    python -m starter_b200.csrc.microbench --kernel attn_decode --rows 8 --context 4096
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+
+import torch
+
+SHAPES = {"qkv": (6144, 2560, False), "o": (2560, 4096, False), "gateup": (9728, 2560, True),
+          "down": (2560, 9728, False), "lm_head": (151936, 2560, False)}
+
+
+def time_graph(calls, replays: int = 5) -> float:
+    """Microseconds per call: the calls are captured in one graph, the median replay is reported."""
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(side):
+        for f in calls[:2]:
+            f()
+    torch.cuda.current_stream().wait_stream(side)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for f in calls:
+            f()
+    graph.replay()
+    torch.cuda.synchronize()
+    times = []
+    for _ in range(replays):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        times.append(a.elapsed_time(b) * 1000.0 / len(calls))
+    return sorted(times)[len(times) // 2]
+
+
+def bench_product(ops, kernel: str, shape: str, rows: int, copies: int):
+    n_out, K, gate_up = SHAPES[shape]
+    w_rows = 2 * n_out if gate_up else n_out
+    copies = min(copies, max(2, (1 << 31) // (w_rows * K * 2)))
+    ws = [torch.randn(w_rows, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
+    a = torch.randn(rows, K, device="cuda", dtype=torch.bfloat16)
+    if kernel == "stream":
+        calls = [lambda w=w: ops._stream_product(a, w, n_out, gate_up, False) for w in ws]
+    elif kernel == "skinny":
+        calls = [lambda w=w: ops._skinny(a, w, n_out, gate_up, False) for w in ws]
+    elif kernel == "cublas":
+        calls = [lambda w=w: torch.mm(a, w.t()) for w in ws]
+    else:
+        raise SystemExit(f"unknown product kernel {kernel!r}")
+    us = time_graph(calls)
+    nbytes = w_rows * K * 2
+    return {"kernel": kernel, "shape": shape, "rows": rows, "us": round(us, 2), "weight_bytes": nbytes,
+            "GB/s": round(nbytes / us / 1e3, 1)}
+
+
+def bench_attn_decode(ops, rows: int, context: int, heads: int, kv_heads: int, head_dim: int, layers: int):
+    from ..cache import Cache, KVRequest
+    from ..engine.context import Runtime, StepContext
+    dtype = torch.bfloat16
+    cache = Cache([KVRequest(kv_heads, head_dim)] * layers, n_slots=rows, max_tokens=rows * context, dtype=dtype,
+                  device="cuda", max_seq_tokens=context)
+    cache.groups[0].k.normal_()
+    cache.groups[0].v.normal_()
+    slots = [cache.alloc() for _ in range(rows)]
+    for s in slots:
+        cache.assume_length(s, context - 1)
+    cache.flush()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    ctx = StepContext(runtime=Runtime(dtype, torch.device("cuda"), ops), cache=cache, n_seqs=rows, n_rows=rows, max_q_len=1,
+                      kv_bound=context, seq_slot=i32(slots), cu_q=i32(list(range(rows + 1))), row_seq=i32(list(range(rows))),
+                      lengths=cache.lengths, status=torch.zeros(1, dtype=torch.int32, device="cuda"))
+    q = torch.randn(rows, heads * head_dim, device="cuda", dtype=dtype)
+    calls = [lambda lc=lc: ops.attention(ctx, q, lc, heads, 1.0 / math.sqrt(head_dim), None) for lc in cache.layers]
+    us = time_graph(calls)
+    nbytes = rows * context * kv_heads * head_dim * 2 * 2
+    return {"kernel": "attn_decode", "rows": rows, "context": context, "us": round(us, 2), "cache_bytes": nbytes,
+            "GB/s": round(nbytes / us / 1e3, 1)}
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--kernel", required=True, choices=["stream", "skinny", "cublas", "attn_decode"])
+    ap.add_argument("--shape", default="gateup", choices=sorted(SHAPES))
+    ap.add_argument("--rows", type=int, default=8)
+    ap.add_argument("--copies", type=int, default=12, help="copies of the weights the graph walks through")
+    ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--layers", type=int, default=8, help="attn_decode: layers of cache the graph walks through")
+    args = ap.parse_args(argv)
+    from .ops import get_ops
+    ops = get_ops(verbose=False)
+    if args.kernel == "attn_decode":
+        out = bench_attn_decode(ops, args.rows, args.context, 32, 8, 128, args.layers)
+    else:
+        out = bench_product(ops, args.kernel, args.shape, args.rows, args.copies)
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())
