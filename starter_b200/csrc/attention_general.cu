@@ -53,6 +53,8 @@ template <class T>
 __global__ void attention_general_kernel(const T* __restrict__ q, T* __restrict__ out, SbBatch batch, SbKV kv,
                                          int n_heads, float scale, int window) {
     __shared__ float qs[AG_MAX_D];
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
     const int D = kv.head_dim;
     const int kvh = head / (n_heads / kv.n_kv_heads);
@@ -117,9 +119,9 @@ extern "C" int sb_attention_general(int dtype, const void* q, void* out, SbBatch
     dim3 grid(batch.n_rows, n_heads);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
     if (dtype == SB_F32)
-        attention_general_kernel<float><<<grid, 32, 0, stream>>>((const float*)q, (float*)out, batch, kv, n_heads, scale, window);
+        sb_launch(attention_general_kernel<float>, grid, 32, 0, stream, (const float*)q, (float*)out, batch, kv, n_heads, scale, window);
     else
-        attention_general_kernel<__nv_bfloat16><<<grid, 32, 0, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch,
+        sb_launch(attention_general_kernel<__nv_bfloat16>, grid, 32, 0, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch,
                                                                          kv, n_heads, scale, window);
     SB_LAUNCH_CHECK();
 }

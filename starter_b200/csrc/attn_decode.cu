@@ -34,6 +34,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
     __shared__ int s_is_last;
     unsigned char* q_s = smem;                             // [16][D] bfloat16
     unsigned char* pipe = smem + 16 * D * 2;               // [warp][stage][K slice | V slice]
+    pdl_launch_dependents();
+    pdl_wait();
 
     const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -276,7 +278,7 @@ template <int D> static int launch_decode(const void* q, void* out, SbBatch batc
         configured = true;
     }
     dim3 grid(batch.n_seqs, kv.n_kv_heads, n_splits);
-    attn_decode_kernel<D><<<grid, AD_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv,
+    sb_launch(attn_decode_kernel<D>, grid, AD_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv,
                                                                  n_heads, scale * 1.4426950408889634f, window, n_splits,
                                                                  partial, counters);
     return (int)cudaGetLastError();

@@ -31,6 +31,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* q_s = smem;                  // [64][D]
     unsigned char* kv_s = smem + AP_ROWS * D * 2;  // [2 stages][K tile | V tile]
+    pdl_launch_dependents();
+    pdl_wait();
 
     const int seq = blockIdx.z, kvh = blockIdx.y;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -213,7 +215,7 @@ template <int D> static int launch_prefill(const void* q, void* out, SbBatch bat
     const long long tiles = ((long long)max_q_len * G + AP_ROWS - 1) / AP_ROWS;
     if (tiles > 2147483647LL || kv.n_kv_heads > 65535 || batch.n_seqs > 65535) return (int)cudaErrorInvalidValue;
     dim3 grid((unsigned int)tiles, kv.n_kv_heads, batch.n_seqs);
-    attn_prefill_kernel<D><<<grid, AP_WARPS * 32, smem, stream>>>((const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv,
+    sb_launch(attn_prefill_kernel<D>, grid, AP_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv,
                                                                   n_heads, scale * 1.4426950408889634f, window);
     return (int)cudaGetLastError();
 }

@@ -94,4 +94,29 @@ __device__ __forceinline__ long long kv_offset(const SbKV& kv, int slot, int pos
     return (((long long)page * kv.n_kv_heads + kv_head) * SB_PAGE + (pos % SB_PAGE)) * kv.head_dim;
 }
 
+// Programmatic dependent launch.  A kernel launched with the attribute may start while the kernel before
+// it in the stream is still running; it must call pdl_wait() before it reads anything that kernel
+// wrote (or writes anything that kernel reads).  What comes before the wait (fetching weights, setting
+// up barriers) overlaps the predecessor's tail.  pdl_launch_dependents() lets the next kernel in the
+// stream start its own preamble.  Without the attribute both are no-ops.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+extern int sb_pdl_flag;  // set through sb_set_pdl(); defined in rows.cu
+
+template <typename... Exp, typename... Act>
+static inline void sb_launch(void (*kernel)(Exp...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Act&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = attr;
+    config.numAttrs = sb_pdl_flag ? 1 : 0;
+    cudaLaunchKernelEx(&config, kernel, static_cast<Act&&>(args)...);
+}
+
 #define SB_LAUNCH_CHECK() return (int)cudaGetLastError()

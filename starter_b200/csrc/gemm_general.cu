@@ -16,6 +16,8 @@ __global__ void __launch_bounds__(256) gemm_general_kernel(const TA* __restrict_
                                                            TO* __restrict__ C, int M, int N, int K) {
     __shared__ float As[GG_BK][GG_BM + 4];
     __shared__ float Ws[GG_BK][GG_BN + 4];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * GG_BM, n0 = blockIdx.x * GG_BN;
     const int tx = tid % 16, ty = tid / 16;  // thread computes rows ty*4.., cols tx*4..
@@ -67,12 +69,12 @@ extern "C" int sb_gemm_general(int dtype, int out_f32, const void* A, const void
     dim3 grid((N + GG_BN - 1) / GG_BN, (M + GG_BM - 1) / GG_BM);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
     if (dtype == SB_F32)
-        gemm_general_kernel<float, float><<<grid, 256, 0, stream>>>((const float*)A, (const float*)W, (float*)C, M, N, K);
+        sb_launch(gemm_general_kernel<float, float>, grid, 256, 0, stream, (const float*)A, (const float*)W, (float*)C, M, N, K);
     else if (out_f32)
-        gemm_general_kernel<__nv_bfloat16, float><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)A, (const __nv_bfloat16*)W,
+        sb_launch(gemm_general_kernel<__nv_bfloat16, float>, grid, 256, 0, stream, (const __nv_bfloat16*)A, (const __nv_bfloat16*)W,
                                                                            (float*)C, M, N, K);
     else
-        gemm_general_kernel<__nv_bfloat16, __nv_bfloat16><<<grid, 256, 0, stream>>>(
+        sb_launch(gemm_general_kernel<__nv_bfloat16, __nv_bfloat16>, grid, 256, 0, stream, 
             (const __nv_bfloat16*)A, (const __nv_bfloat16*)W, (__nv_bfloat16*)C, M, N, K);
     SB_LAUNCH_CHECK();
 }

@@ -104,9 +104,11 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     };
     constexpr int STRIDE = WPG * GS_KWARP;
     int kt = k_begin + wk * GS_KWARP;
+    pdl_launch_dependents();
     if (DEEP) {
         uint4 lo_a[4], hi_a[4], lo_b[4], hi_b[4];
         if (kt < k_end) load_w(lo_a, hi_a, kt);
+        pdl_wait();
         while (kt < k_end) {
             if (kt + STRIDE < k_end) load_w(lo_b, hi_b, kt + STRIDE);
             turn(lo_a, hi_a, kt);
@@ -117,10 +119,14 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
             kt += STRIDE;
         }
     } else {
+        // The weights do not depend on the kernel before this one: the first turn's are requested
+        // before the wait for that kernel, the activations after it.
+        uint4 lo[4], hi[4];
+        if (kt < k_end) load_w(lo, hi, kt);
+        pdl_wait();
         for (; kt < k_end; kt += STRIDE) {
-            uint4 lo[4], hi[4];
-            load_w(lo, hi, kt);
             turn(lo, hi, kt);
+            if (kt + STRIDE < k_end) load_w(lo, hi, kt + STRIDE);
         }
     }
 
@@ -206,10 +212,10 @@ int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int 
 #define SB_SKINNY(NT, GU)                                                                                              \
     do {                                                                                                               \
         if (deep)                                                                                                      \
-            gemm_skinny_kernel<NT, GU, true><<<grid, GS_WARPS * 32, 0, stream>>>(a, w, C, M, n_out, K, k_per_split,      \
+            sb_launch(gemm_skinny_kernel<NT, GU, true>, grid, GS_WARPS * 32, 0, stream, a, w, C, M, n_out, K, k_per_split,      \
                                                                                n_splits, out_f32, partial, counters); \
         else                                                                                                           \
-            gemm_skinny_kernel<NT, GU, false><<<grid, GS_WARPS * 32, 0, stream>>>(a, w, C, M, n_out, K, k_per_split,     \
+            sb_launch(gemm_skinny_kernel<NT, GU, false>, grid, GS_WARPS * 32, 0, stream, a, w, C, M, n_out, K, k_per_split,     \
                                                                                 n_splits, out_f32, partial, counters);\
     } while (0)
     if (M <= 8) {

@@ -183,13 +183,27 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
 
     if (warp == 0 && lane == 0) {
         // ---- producer: one TMA box of W (two with GATE_UP) and one of the activations per unit ----
-        int stage = 0;
-        uint32_t phase = 0;
+        // The weights do not depend on the kernel before this one: the first ring of stages is
+        // requested before the wait for that kernel, the activations of those stages after it.
+        const int pre = (int)min((long long)STAGES, u1 - u0);
+        for (int i = 0; i < pre; ++i) {
+            const long long u = u0 + i;
+            const int tile = (int)(u / args.k_blocks), kb = (int)(u % args.k_blocks);
+            mbar_expect_tx(&full[i], N_A * A_BYTES + B_BYTES);
+            tma_load_2d(a_s + (i * N_A) * A_BYTES, &map_w, kb * ST_BK, tile * ST_BM, &full[i]);
+            if (GATE_UP) tma_load_2d(a_s + (i * N_A + 1) * A_BYTES, &map_w2, kb * ST_BK, tile * ST_BM, &full[i]);
+        }
+        pdl_wait();
+        for (int i = 0; i < pre; ++i)
+            tma_load_2d(b_s + i * B_BYTES, &map_a, (int)((u0 + i) % args.k_blocks) * ST_BK, 0, &full[i]);
+        int stage = pre % STAGES;
+        uint32_t phase = pre == STAGES ? 1 : 0;
         bool ok = true;
-        for (long long u = u0; u < u1 && ok; ++u) {
+        for (long long u = u0 + pre; u < u1 && ok; ++u) {
             const int tile = (int)(u / args.k_blocks), kb = (int)(u % args.k_blocks);
             ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, args.status);
             if (!ok) break;
@@ -207,6 +221,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
     } else if (warp == 1 && lane == 0) {
         // ---- MMA issuer ----
+        pdl_wait();
         const uint32_t idesc = umma_idesc(BN);
         int stage = 0;
         uint32_t phase = 0, acc_phase[2] = {0, 0};
@@ -241,6 +256,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         }
     } else if (warp >= 2) {
         // ---- epilogue: warp w drains lanes 32 * (w % 4) .. + 31 of tensor memory = rows of the tile ----
+        pdl_wait();
         const int quarter = warp & 3;
         const int row_in_tile = quarter * 32 + lane;
         uint32_t acc_phase[2] = {0, 0};
@@ -406,7 +422,7 @@ static int launch_stream(const CUtensorMap& mw, const CUtensorMap& mw2, const CU
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    gemm_stream_kernel<BN, GU, STAGES><<<grid, ST_THREADS, smem, stream>>>(mw, mw2, ma, args);
+    sb_launch(gemm_stream_kernel<BN, GU, STAGES>, grid, ST_THREADS, smem, stream, mw, mw2, ma, args);
     return (int)cudaGetLastError();
 }
 

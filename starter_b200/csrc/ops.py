@@ -82,6 +82,8 @@ class Ops:
             fn = getattr(lib, name)
             fn.argtypes = argtypes
             fn.restype = c_int
+        lib.sb_set_pdl.argtypes = [c_int]
+        lib.sb_set_pdl.restype = None
         self._scratch = {}
         self._sm_count = None
         self.force_skinny = None  # (K slices, deep) for tuning runs; None = the rules below
@@ -117,6 +119,11 @@ class Ops:
                       g.ring_pages, g.request.num_kv_heads, g.request.head_dim)
             layer_cache._sb_kv = kv
         return kv
+
+    def set_dependent_launch(self, on: bool) -> None:
+        """Launch kernels so that each may start its preamble (weight fetches, barrier set-up) while the
+        one before it in the stream is finishing; see common.cuh."""
+        self.lib.sb_set_pdl(int(bool(on)))
 
     def prepare_matrix(self, w: torch.Tensor) -> torch.Tensor:
         """A weight matrix [out, in] as the products want it: contiguous, in the run's dtype."""

@@ -19,6 +19,8 @@ __global__ void qk_rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
                                      const W* __restrict__ k_norm_w, float eps, const T* __restrict__ cos_t,
                                      const T* __restrict__ sin_t, int rotary_dim, int* status) {
     __shared__ float y[QK_MAX_D];
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
     const int D = kv.head_dim;
     const int width = (n_heads + 2 * n_kv_heads) * D;
@@ -85,7 +87,7 @@ extern "C" int sb_qk_rope_store(int dtype, int wdtype, const void* qkv, void* q_
     dim3 grid(batch.n_rows, n_heads + n_kv_heads);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
 #define SB_QK(T, W)                                                                                                    \
-    qk_rope_store_kernel<T, W><<<grid, 32, 0, stream>>>((const T*)qkv, (T*)q_out, batch, kv, n_heads, n_kv_heads,        \
+    sb_launch(qk_rope_store_kernel<T, W>, grid, 32, 0, stream, (const T*)qkv, (T*)q_out, batch, kv, n_heads, n_kv_heads,        \
                                                         (const W*)q_norm_w, (const W*)k_norm_w, eps, (const T*)cos_t,   \
                                                         (const T*)sin_t, rotary_dim, status)
     if (dtype == SB_F32) {

@@ -11,6 +11,8 @@
 template <class T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table, T* __restrict__ out,
                              int hidden, int vocab, int* status) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int row = blockIdx.x;
     int tok = tokens[row];
     if (tok < 0 || tok >= vocab) {
@@ -24,6 +26,8 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
 
 template <class T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out, int width) {
+    pdl_launch_dependents();
+    pdl_wait();
     const T* src = x + (long long)rows[blockIdx.x] * width;
     T* dst = out + (long long)blockIdx.x * width;
     for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
@@ -34,6 +38,8 @@ template <class T, class W, bool ADD>
 __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, const W* __restrict__ weight,
                                T* __restrict__ out, int width, float eps) {
     __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
     T* xr = x + (long long)blockIdx.x * width;
     const T* dr = ADD ? delta + (long long)blockIdx.x * width : nullptr;
     T* yr = out + (long long)blockIdx.x * width;
@@ -60,6 +66,8 @@ template <class W, bool ADD>
 __global__ void rmsnorm_vec_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
                                    const W* __restrict__ weight, __nv_bfloat16* __restrict__ out, int width, float eps) {
     __shared__ float red[33];
+    pdl_launch_dependents();
+    pdl_wait();
     const long long base = (long long)blockIdx.x * width;
     const int c = threadIdx.x * 8;
     const bool active = c < width;
@@ -110,6 +118,8 @@ __global__ void rmsnorm_vec_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfl
 
 template <class T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
+    pdl_launch_dependents();
+    pdl_wait();
     const long long row = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
     if (c >= inter) return;
@@ -120,6 +130,8 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 }
 
 __global__ void advance_lengths_kernel(SbBatch b, int* lengths) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int s = blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= b.n_seqs) return;
     const int slot = b.seq_slot[s];
@@ -132,15 +144,20 @@ static inline int row_threads(int width) {
     return t;
 }
 
+int sb_pdl_flag = 0;
+
 extern "C" {
+
+// 1: launch every kernel of this library with programmatic dependent launch; 0: plain stream order.
+void sb_set_pdl(int on) { sb_pdl_flag = on ? 1 : 0; }
 
 int sb_embed(int dtype, const int* tokens, const void* table, void* out, int rows, int hidden, int vocab, int* status,
              cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (dtype == SB_F32)
-        embed_kernel<float><<<rows, row_threads(hidden), 0, stream>>>(tokens, (const float*)table, (float*)out, hidden, vocab, status);
+        sb_launch(embed_kernel<float>, rows, row_threads(hidden), 0, stream, tokens, (const float*)table, (float*)out, hidden, vocab, status);
     else
-        embed_kernel<__nv_bfloat16><<<rows, row_threads(hidden), 0, stream>>>(tokens, (const __nv_bfloat16*)table,
+        sb_launch(embed_kernel<__nv_bfloat16>, rows, row_threads(hidden), 0, stream, tokens, (const __nv_bfloat16*)table,
                                                                                 (__nv_bfloat16*)out, hidden, vocab, status);
     SB_LAUNCH_CHECK();
 }
@@ -148,9 +165,9 @@ int sb_embed(int dtype, const int* tokens, const void* table, void* out, int row
 int sb_gather_rows(int dtype, const void* x, const int* rows, void* out, int n_rows, int width, cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (dtype == SB_F32)
-        gather_rows_kernel<float><<<n_rows, row_threads(width), 0, stream>>>((const float*)x, rows, (float*)out, width);
+        sb_launch(gather_rows_kernel<float>, n_rows, row_threads(width), 0, stream, (const float*)x, rows, (float*)out, width);
     else
-        gather_rows_kernel<__nv_bfloat16><<<n_rows, row_threads(width), 0, stream>>>((const __nv_bfloat16*)x, rows,
+        sb_launch(gather_rows_kernel<__nv_bfloat16>, n_rows, row_threads(width), 0, stream, (const __nv_bfloat16*)x, rows,
                                                                                       (__nv_bfloat16*)out, width);
     SB_LAUNCH_CHECK();
 }
@@ -163,9 +180,9 @@ int sb_rmsnorm(int dtype, int wdtype, void* x, const void* delta, const void* we
 #define SB_NORM(T, W)                                                                                             \
     do {                                                                                                          \
         if (delta)                                                                                                \
-            rmsnorm_kernel<T, W, true><<<rows, th, 0, stream>>>((T*)x, (const T*)delta, (const W*)weight, (T*)out, width, eps); \
+            sb_launch(rmsnorm_kernel<T, W, true>, rows, th, 0, stream, (T*)x, (const T*)delta, (const W*)weight, (T*)out, width, eps); \
         else                                                                                                      \
-            rmsnorm_kernel<T, W, false><<<rows, th, 0, stream>>>((T*)x, nullptr, (const W*)weight, (T*)out, width, eps);        \
+            sb_launch(rmsnorm_kernel<T, W, false>, rows, th, 0, stream, (T*)x, nullptr, (const W*)weight, (T*)out, width, eps);        \
     } while (0)
     if (dtype == SB_F32) {
         if (wdtype != SB_F32) return (int)cudaErrorInvalidValue;
@@ -175,10 +192,10 @@ int sb_rmsnorm(int dtype, int wdtype, void* x, const void* delta, const void* we
 #define SB_VNORM(W)                                                                                                  \
     do {                                                                                                             \
         if (delta)                                                                                                   \
-            rmsnorm_vec_kernel<W, true><<<rows, vt, 0, stream>>>((__nv_bfloat16*)x, (const __nv_bfloat16*)delta,      \
+            sb_launch(rmsnorm_vec_kernel<W, true>, rows, vt, 0, stream, (__nv_bfloat16*)x, (const __nv_bfloat16*)delta,      \
                                                                   (const W*)weight, (__nv_bfloat16*)out, width, eps); \
         else                                                                                                         \
-            rmsnorm_vec_kernel<W, false><<<rows, vt, 0, stream>>>((__nv_bfloat16*)x, nullptr, (const W*)weight,       \
+            sb_launch(rmsnorm_vec_kernel<W, false>, rows, vt, 0, stream, (__nv_bfloat16*)x, nullptr, (const W*)weight,       \
                                                                    (__nv_bfloat16*)out, width, eps);                 \
     } while (0)
         if (wdtype == SB_F32) SB_VNORM(float); else SB_VNORM(__nv_bfloat16);
@@ -196,15 +213,15 @@ int sb_swiglu(int dtype, const void* gu, void* out, int rows, int inter, cudaStr
     if (rows <= 0) return 0;
     dim3 grid(rows, (inter + 255) / 256);
     if (dtype == SB_F32)
-        swiglu_kernel<float><<<grid, 256, 0, stream>>>((const float*)gu, (float*)out, inter);
+        sb_launch(swiglu_kernel<float>, grid, 256, 0, stream, (const float*)gu, (float*)out, inter);
     else
-        swiglu_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter);
+        sb_launch(swiglu_kernel<__nv_bfloat16>, grid, 256, 0, stream, (const __nv_bfloat16*)gu, (__nv_bfloat16*)out, inter);
     SB_LAUNCH_CHECK();
 }
 
 int sb_advance_lengths(SbBatch b, int* lengths, cudaStream_t stream) {
     if (b.n_seqs <= 0) return 0;
-    advance_lengths_kernel<<<(b.n_seqs + 127) / 128, 128, 0, stream>>>(b, lengths);
+    sb_launch(advance_lengths_kernel, (b.n_seqs + 127) / 128, 128, 0, stream, b, lengths);
     SB_LAUNCH_CHECK();
 }
 

@@ -48,6 +48,8 @@ __global__ void argmax_kernel(const float* __restrict__ values, const int* __res
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const int chunks = gridDim.y;
+    pdl_launch_dependents();
+    pdl_wait();
     const int per = (n + chunks - 1) / chunks;
     const int begin = blockIdx.y * per, end = min(n, begin + per);
     const float* row = values + (long long)blockIdx.x * row_stride;
@@ -118,6 +120,8 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
     __shared__ unsigned int s_prefix;
     __shared__ int s_need;
     __shared__ int s_token;
+    pdl_launch_dependents();
+    pdl_wait();
     const float* row = logits + (long long)blockIdx.x * vocab;
     const int tid = threadIdx.x;
     const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
@@ -228,10 +232,10 @@ int sb_argmax(const float* logits, int* out, int rows, int vocab, float* scratch
     if (rows <= 0) return 0;
     const int chunks = vocab >= 16384 ? 32 : 1;
     if (chunks == 1) {
-        argmax_kernel<<<dim3(rows, 1), 1024, 0, stream>>>(logits, nullptr, vocab, vocab, nullptr, out);
+        sb_launch(argmax_kernel, dim3(rows, 1), 1024, 0, stream, logits, nullptr, vocab, vocab, nullptr, out);
     } else {
-        argmax_kernel<<<dim3(rows, chunks), 512, 0, stream>>>(logits, nullptr, vocab, vocab, scratch_v, scratch_i);
-        argmax_kernel<<<dim3(rows, 1), 32, 0, stream>>>(scratch_v, scratch_i, chunks, chunks, nullptr, out);
+        sb_launch(argmax_kernel, dim3(rows, chunks), 512, 0, stream, logits, nullptr, vocab, vocab, scratch_v, scratch_i);
+        sb_launch(argmax_kernel, dim3(rows, 1), 32, 0, stream, scratch_v, scratch_i, chunks, chunks, nullptr, out);
     }
     SB_LAUNCH_CHECK();
 }
@@ -242,7 +246,7 @@ int sb_sample(const float* logits, int* out, int rows, int vocab, float temperat
               const int* request_ids, int* steps, int advance, cudaStream_t stream) {
     if (rows <= 0) return 0;
     if (!(temperature > 0.f)) return (int)cudaErrorInvalidValue;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, stream>>>(logits, out, vocab, temperature, top_k, seed, request_ids, steps, advance);
+    sb_launch(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, out, vocab, temperature, top_k, seed, request_ids, steps, advance);
     SB_LAUNCH_CHECK();
 }
 

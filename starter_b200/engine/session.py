@@ -2,6 +2,7 @@
 
 from __future__ import annotations
 
+import os
 from typing import Optional
 
 import torch
@@ -34,11 +35,13 @@ class Session:
     hold together, each rounded up to the page size; ``max_seqs``: how many
     sequences may be live at once; ``max_seq_tokens``: the longest sequence.
     ``ops``: the kernel call table; by default the CUDA extension, which must load.
+    ``dependent_launch``: let each kernel start its preamble while its predecessor finishes
+    (programmatic dependent launch); on by default, off with STARTER_B200_NO_PDL in the environment.
     """
 
     def __init__(self, model, dtype="bfloat16", max_tokens: int = 8192, max_seqs: Optional[int] = None,
                  max_seq_tokens: Optional[int] = None, max_step_tokens: int = 1024, max_rows: int = 8192,
-                 device="cuda:0", ops=None, verbose: bool = True):
+                 device="cuda:0", ops=None, verbose: bool = True, dependent_launch=None):
         self.dtype = parse_dtype(dtype)
         self.device = torch.device(device)
         if ops is None:
@@ -47,6 +50,10 @@ class Session:
                 raise ValueError("the kernels of this library run on a CUDA device only")
             torch.cuda.set_device(self.device)
             ops = get_ops(verbose=verbose)
+        if dependent_launch is None:
+            dependent_launch = os.environ.get("STARTER_B200_NO_PDL") is None
+        if hasattr(ops, "set_dependent_launch"):
+            ops.set_dependent_launch(dependent_launch)
         self.runtime = Runtime(dtype=self.dtype, device=self.device, ops=ops)
         if isinstance(model, tuple):
             config, source = model
