@@ -53,7 +53,6 @@ template <class T>
 __global__ void attention_general_kernel(const T* __restrict__ q, T* __restrict__ out, SbBatch batch, SbKV kv,
                                          int n_heads, float scale, int window) {
     __shared__ float qs[AG_MAX_D];
-    pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
     const int D = kv.head_dim;

@@ -34,7 +34,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
     __shared__ int s_is_last;
     unsigned char* q_s = smem;                             // [16][D] bfloat16
     unsigned char* pipe = smem + 16 * D * 2;               // [warp][stage][K slice | V slice]
-    pdl_launch_dependents();
     pdl_wait();
 
     const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
@@ -157,6 +156,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
         __syncwarp();
     }
     cp_async_wait<0>();
+    pdl_launch_dependents();   // the keys are read; the next kernel may set itself up during the merge
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);

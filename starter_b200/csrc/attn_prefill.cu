@@ -31,7 +31,6 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
     extern __shared__ __align__(128) unsigned char smem[];
     unsigned char* q_s = smem;                  // [64][D]
     unsigned char* kv_s = smem + AP_ROWS * D * 2;  // [2 stages][K tile | V tile]
-    pdl_launch_dependents();
     pdl_wait();
 
     const int seq = blockIdx.z, kvh = blockIdx.y;
@@ -179,6 +178,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
         __syncthreads();  // everyone is done with this stage before the copy after next lands in it
     }
     cp_async_wait<0>();
+    pdl_launch_dependents();
 
 #pragma unroll
     for (int h = 0; h < 2; ++h) {

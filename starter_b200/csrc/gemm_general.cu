@@ -16,7 +16,6 @@ __global__ void __launch_bounds__(256) gemm_general_kernel(const TA* __restrict_
                                                            TO* __restrict__ C, int M, int N, int K) {
     __shared__ float As[GG_BK][GG_BM + 4];
     __shared__ float Ws[GG_BK][GG_BN + 4];
-    pdl_launch_dependents();
     pdl_wait();
     const int tid = threadIdx.x;
     const int m0 = blockIdx.y * GG_BM, n0 = blockIdx.x * GG_BN;

@@ -104,7 +104,6 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     };
     constexpr int STRIDE = WPG * GS_KWARP;
     int kt = k_begin + wk * GS_KWARP;
-    pdl_launch_dependents();
     if (DEEP) {
         uint4 lo_a[4], hi_a[4], lo_b[4], hi_b[4];
         if (kt < k_end) load_w(lo_a, hi_a, kt);
@@ -130,6 +129,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         }
     }
 
+    pdl_launch_dependents();   // the weights are read; the next kernel may start fetching its own
     // Warps meet: red[warp][weight row][activation row].
 #pragma unroll
     for (int t = 0; t < NT; ++t) {

@@ -183,7 +183,6 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_launch_dependents();
 
     if (warp == 0 && lane == 0) {
         // ---- producer: one TMA box of W (two with GATE_UP) and one of the activations per unit ----
@@ -213,6 +212,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             tma_load_2d(b_s + stage * B_BYTES, &map_a, kb * ST_BK, 0, &full[stage]);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
+        pdl_launch_dependents();   // every load of this block is requested: the next kernel may start fetching
         if (!ok) {
             // Leaving early: give the copies already requested a bounded time to land before the block's
             // shared memory goes away.

@@ -11,6 +11,7 @@ the compiled library, ``get_ops`` raises.
 from __future__ import annotations
 
 import ctypes
+import os
 from ctypes import POINTER, Structure, c_float, c_int, c_ulonglong, c_void_p
 
 import torch
@@ -87,7 +88,7 @@ class Ops:
         self._scratch = {}
         self._sm_count = None
         self.force_skinny = None  # (K slices, deep) for tuning runs; None = the rules below
-        self.use_stream = True    # the TMA + tcgen05 weight-streaming product for decode-sized rows
+        self.use_stream = os.environ.get("STARTER_B200_STREAM", "1") != "0"  # the TMA + tcgen05 product for decode
         self._kernel_status = None
 
     # ---- plumbing -----------------------------------------------------------------------

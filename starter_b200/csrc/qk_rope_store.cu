@@ -19,7 +19,6 @@ __global__ void qk_rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
                                      const W* __restrict__ k_norm_w, float eps, const T* __restrict__ cos_t,
                                      const T* __restrict__ sin_t, int rotary_dim, int* status) {
     __shared__ float y[QK_MAX_D];
-    pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
     const int D = kv.head_dim;

@@ -11,7 +11,6 @@
 template <class T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table, T* __restrict__ out,
                              int hidden, int vocab, int* status) {
-    pdl_launch_dependents();
     pdl_wait();
     const int row = blockIdx.x;
     int tok = tokens[row];
@@ -26,7 +25,6 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
 
 template <class T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out, int width) {
-    pdl_launch_dependents();
     pdl_wait();
     const T* src = x + (long long)rows[blockIdx.x] * width;
     T* dst = out + (long long)blockIdx.x * width;
@@ -38,7 +36,6 @@ template <class T, class W, bool ADD>
 __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, const W* __restrict__ weight,
                                T* __restrict__ out, int width, float eps) {
     __shared__ float red[33];
-    pdl_launch_dependents();
     pdl_wait();
     T* xr = x + (long long)blockIdx.x * width;
     const T* dr = ADD ? delta + (long long)blockIdx.x * width : nullptr;
@@ -66,7 +63,6 @@ template <class W, bool ADD>
 __global__ void rmsnorm_vec_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
                                    const W* __restrict__ weight, __nv_bfloat16* __restrict__ out, int width, float eps) {
     __shared__ float red[33];
-    pdl_launch_dependents();
     pdl_wait();
     const long long base = (long long)blockIdx.x * width;
     const int c = threadIdx.x * 8;
@@ -118,7 +114,6 @@ __global__ void rmsnorm_vec_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfl
 
 template <class T>
 __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int inter) {
-    pdl_launch_dependents();
     pdl_wait();
     const long long row = blockIdx.x;
     const int c = blockIdx.y * blockDim.x + threadIdx.x;
@@ -130,7 +125,6 @@ __global__ void swiglu_kernel(const T* __restrict__ gu, T* __restrict__ out, int
 }
 
 __global__ void advance_lengths_kernel(SbBatch b, int* lengths) {
-    pdl_launch_dependents();
     pdl_wait();
     const int s = blockIdx.x * blockDim.x + threadIdx.x;
     if (s >= b.n_seqs) return;

@@ -48,7 +48,6 @@ __global__ void argmax_kernel(const float* __restrict__ values, const int* __res
     __shared__ float best_v[32];
     __shared__ int best_i[32];
     const int chunks = gridDim.y;
-    pdl_launch_dependents();
     pdl_wait();
     const int per = (n + chunks - 1) / chunks;
     const int begin = blockIdx.y * per, end = min(n, begin + per);
@@ -120,7 +119,6 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
     __shared__ unsigned int s_prefix;
     __shared__ int s_need;
     __shared__ int s_token;
-    pdl_launch_dependents();
     pdl_wait();
     const float* row = logits + (long long)blockIdx.x * vocab;
     const int tid = threadIdx.x;
