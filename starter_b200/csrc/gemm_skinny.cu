@@ -118,14 +118,13 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
             kt += STRIDE;
         }
     } else {
-        // The weights do not depend on the kernel before this one: the first turn's are requested
-        // before the wait for that kernel, the activations after it.
-        uint4 lo[4], hi[4];
-        if (kt < k_end) load_w(lo, hi, kt);
-        pdl_wait();
+        // The weights do not depend on the kernel before this one: a turn's weights are requested
+        // before the wait for that kernel (which matters in the first turn only), the activations after it.
         for (; kt < k_end; kt += STRIDE) {
+            uint4 lo[4], hi[4];
+            load_w(lo, hi, kt);
+            pdl_wait();
             turn(lo, hi, kt);
-            if (kt + STRIDE < k_end) load_w(lo, hi, kt + STRIDE);
         }
     }
 

@@ -96,9 +96,11 @@ def main(argv=None) -> int:
     ap.add_argument("--copies", type=int, default=12, help="copies of the weights the graph walks through")
     ap.add_argument("--context", type=int, default=4096)
     ap.add_argument("--layers", type=int, default=8, help="attn_decode: layers of cache the graph walks through")
+    ap.add_argument("--dependent-launch", action="store_true", help="launch with programmatic dependent launch")
     args = ap.parse_args(argv)
     from .ops import get_ops
     ops = get_ops(verbose=False)
+    ops.set_dependent_launch(args.dependent_launch)
     if args.kernel == "attn_decode":
         out = bench_attn_decode(ops, args.rows, args.context, 32, 8, 128, args.layers)
     else:
