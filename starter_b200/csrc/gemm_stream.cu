@@ -131,7 +131,16 @@ struct StreamArgs {
     int M, n_out, K;
     int n_tiles, k_blocks, max_parts;
     int out_f32;
+    long long* timeline;  // when not null: [block][16] globaltimer stamps of the block's milestones (for tuning)
 };
+
+__device__ __forceinline__ void stamp(const StreamArgs& args, int slot) {
+    if (args.timeline) {
+        long long t;
+        asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t));
+        args.timeline[blockIdx.x * 16 + slot] = t;
+    }
+}
 
 // Units [u0, u1) of block c out of P, with U units in all.
 __device__ __forceinline__ long long unit_begin(long long c, long long U, long long P) { return c * U / P; }
@@ -171,6 +180,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
     const long long u0 = unit_begin(blockIdx.x, U, P), u1 = unit_begin(blockIdx.x + 1, U, P);
 
     if (threadIdx.x == 0) {
+        stamp(args, 0);
         for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
         for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
         *abort_flag = 0;
@@ -196,7 +206,9 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             tma_load_2d(a_s + (i * N_A) * A_BYTES, &map_w, kb * ST_BK, tile * ST_BM, &full[i]);
             if (GATE_UP) tma_load_2d(a_s + (i * N_A + 1) * A_BYTES, &map_w2, kb * ST_BK, tile * ST_BM, &full[i]);
         }
+        stamp(args, 1);
         pdl_wait();
+        stamp(args, 2);
         for (int i = 0; i < pre; ++i)
             tma_load_2d(b_s + i * B_BYTES, &map_a, (int)((u0 + i) % args.k_blocks) * ST_BK, 0, &full[i]);
         int stage = pre % STAGES;
@@ -212,6 +224,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             tma_load_2d(b_s + stage * B_BYTES, &map_a, kb * ST_BK, 0, &full[stage]);
             if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
+        stamp(args, 3);
         pdl_launch_dependents();   // every load of this block is requested: the next kernel may start fetching
         if (!ok) {
             // Leaving early: give the copies already requested a bounded time to land before the block's
@@ -239,6 +252,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             for (int i = 0; i < n_kb && ok; ++i) {
                 ok = mbar_wait(&full[stage], phase, abort_flag, args.status);
                 if (!ok) break;
+                if (item == 0 && i == 0) stamp(args, 5);
                 tc_fence_after();
                 const uint64_t b_desc = umma_desc(b_s + stage * B_BYTES);
 #pragma unroll
@@ -254,6 +268,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             if (ok) tc_commit(&acc_full[buf]);
             u += n_kb;
         }
+        stamp(args, 4);
     } else if (warp >= 2) {
         // ---- epilogue: warp w drains lanes 32 * (w % 4) .. + 31 of tensor memory = rows of the tile ----
         pdl_wait();
@@ -272,6 +287,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             asm volatile("bar.sync 1, 128;" ::: "memory");
             ok = wait_flag[buf] != 0;
             if (!ok) break;
+            if (threadIdx.x == 64) stamp(args, 8);
             acc_phase[buf] ^= 1;
             tc_fence_after();
             const uint32_t taddr = tmem_base + ((uint32_t)(quarter * 32) << 16) + buf * ACC_COLS;
@@ -314,16 +330,22 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             tc_fence_before();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buf]);   // the MMA thread may reuse this accumulator
+            if (threadIdx.x == 64) stamp(args, 9);
             if (!whole) {
                 // The last block to finish its share of this tile adds the shares up, in the order of the
                 // blocks, so the sum does not depend on who came last.
-                __threadfence();
+                // (The barrier orders the 128 threads' stores before thread 64's fence, and that fence is
+                // cumulative: one fence at GPU scope publishes the whole block's share.)
                 asm volatile("bar.sync 1, 128;" ::: "memory");
-                if (threadIdx.x == 64) *last_flag = atomicAdd(&args.counters[tile], 1) == parts - 1;
+                if (threadIdx.x == 64) {
+                    __threadfence();
+                    *last_flag = atomicAdd(&args.counters[tile], 1) == parts - 1;
+                    __threadfence();
+                }
                 asm volatile("bar.sync 1, 128;" ::: "memory");
                 const bool last = *last_flag != 0;
+                if (threadIdx.x == 64) stamp(args, 10);
                 if (last) {
-                    __threadfence();
                     const float* base = args.partial + (((long long)tile * args.max_parts) * ST_BM + row_in_tile) * ACC_COLS;
                     const long long part_stride = (long long)ST_BM * ACC_COLS;
                     for (int c0 = 0; c0 < BN && c0 < args.M; c0 += 8) {
@@ -367,14 +389,17 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
                     }
                     if (threadIdx.x == 64) args.counters[tile] = 0;
                 }
+                if (threadIdx.x == 64) stamp(args, last ? 11 : 12);
                 asm volatile("bar.sync 1, 128;" ::: "memory");   // last_flag is read before the next item writes it
             }
             u += n_kb;
         }
     }
+    if (threadIdx.x == 64) stamp(args, 6);
     tc_fence_before();
     __syncthreads();
     if (warp == 1) tmem_dealloc(tmem_base, TMEM_COLS);
+    if (threadIdx.x == 0) stamp(args, 7);
 }
 
 // ---- host side ----------------------------------------------------------------------------------
@@ -444,6 +469,9 @@ int sb_gemm_stream_plan(int n_out, int K, int n_sms, int* grid, int* n_tiles, in
 
 // A [M, K], W [n_out, K] (or [2 * n_out, K], gate rows first, with gate_up), C [M, n_out] bfloat16 or float.
 // M <= 64, K a multiple of 8.  grid, max_parts from sb_gemm_stream_plan.
+static long long* stream_timeline = nullptr;
+void sb_gemm_stream_timeline(long long* buffer) { stream_timeline = buffer; }
+
 int sb_gemm_stream(const void* A, const void* W, void* C, int M, int n_out, int K, int gate_up, int out_f32, int grid,
                    int max_parts, float* partial, int* counters, int* status, cudaStream_t stream) {
     if (M <= 0 || n_out <= 0) return 0;
@@ -463,6 +491,7 @@ int sb_gemm_stream(const void* A, const void* W, void* C, int M, int n_out, int 
     args.k_blocks = (K + ST_BK - 1) / ST_BK;
     args.max_parts = max_parts;
     args.out_f32 = out_f32;
+    args.timeline = stream_timeline;
     if (gate_up) {
         if (bn == 16) return launch_stream<16, true, 6>(mw, mw2, ma, args, grid, stream);
         return launch_stream<32, true, 5>(mw, mw2, ma, args, grid, stream);

@@ -179,7 +179,7 @@ class Ops:
 
     SKINNY_MAX_ROWS = 8   # up to 16 run, but cuBLAS is faster from 9 rows on
     STREAM_MAX_ROWS = 64
-    STREAM_MIN_WORK = 1 << 22   # rows of W times K below which the simpler kernels do as well
+    STREAM_MIN_WORK = int(os.environ.get("STARTER_B200_STREAM_MIN", 40_000_000))  # elements of W below which the simpler kernels do as well
 
     def kernel_status(self, device) -> torch.Tensor:
         """A status word of the kernels that are not tied to a step (bit 4: a wait inside a kernel timed out)."""
@@ -217,7 +217,7 @@ class Ops:
 
     def _takes_stream(self, M, n_out, K, gate_up) -> bool:
         return (self.use_stream and M <= (32 if gate_up else self.STREAM_MAX_ROWS) and K % 8 == 0 and K >= 64
-                and n_out * K >= self.STREAM_MIN_WORK)
+                and n_out * K * (2 if gate_up else 1) >= self.STREAM_MIN_WORK)
 
     def skinny_splits(self, blocks: int, K: int) -> int:
         """K slices per block of 16 weight rows: enough blocks for three per SM, but no slice
