@@ -74,6 +74,8 @@ class Ops:
                                c_void_p, c_void_p],
             "sb_gemm_stream_plan": [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int)],
             "sb_attn_prefill": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p],
+            "sb_attn_decode_balanced": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
+                                        c_void_p],
             "sb_attn_decode": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
@@ -90,6 +92,7 @@ class Ops:
         self.force_skinny = None  # (K slices, deep) for tuning runs; None = the rules below
         self.use_stream = os.environ.get("STARTER_B200_STREAM", "1") != "0"  # the TMA + tcgen05 product for decode
         self._kernel_status = None
+        self.decode_balanced = os.environ.get("STARTER_B200_ATTN", "balanced") != "split"
 
     # ---- plumbing -----------------------------------------------------------------------
 
@@ -332,7 +335,21 @@ class Ops:
         out = torch.empty_like(q)
         kv = self._kv(layer_cache)
         if q.dtype == torch.bfloat16 and kv.head_dim in (64, 128):
-            if ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and n_heads // kv.n_kv_heads <= 16:
+            if (ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and n_heads // kv.n_kv_heads <= 16 and self.decode_balanced
+                    and ctx.n_seqs <= 1024):
+                # as many blocks as the GPU holds at once (three per SM at head size 128), each with an equal share of pages
+                grid = min((3 if kv.head_dim > 64 else 4) * self.sm_count(), 512)
+                key = ("attn_decode_balanced", q.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, grid)
+                buf = self._scratch.get(key)
+                if buf is None:
+                    pairs = ctx.n_seqs * kv.n_kv_heads
+                    floats = (pairs + grid) * (n_heads // kv.n_kv_heads) * (kv.head_dim + 2)
+                    buf = self._scratch[key] = (torch.empty(floats, dtype=torch.float32, device=q.device),
+                                                torch.zeros(pairs, dtype=torch.int32, device=q.device))
+                self._check(self.lib.sb_attn_decode_balanced(_ptr(q), _ptr(out), self._batch(ctx), kv, n_heads, scale,
+                                                             int(window or 0), grid, _ptr(buf[0]), _ptr(buf[1]),
+                                                             self._stream()), "attn_decode_balanced")
+            elif ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and n_heads // kv.n_kv_heads <= 16:
                 g = layer_cache.group
                 n_splits = self.decode_splits(ctx.n_seqs, kv.n_kv_heads, g.table_width, kv.head_dim)
                 partial, counters = self._decode_scratch(q.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, n_splits)
