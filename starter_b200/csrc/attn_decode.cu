@@ -68,11 +68,18 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
     const __nv_bfloat16* vbase = (const __nv_bfloat16*)kv.v;
     const int* table = kv.table + (long long)slot * kv.table_width;
 
+    // The ids of the block's pages, 32 at a time, one per lane: a lookup in the page table costs a trip to
+    // L2, and paying it for every page would stall the copies behind it.
+    int page_ids = 0;
     auto issue = [&](int i) {  // bring this warp's keys and values of the block's i-th page into stage i % STAGES
         if (i < my_pages) {
-            int lp = p_begin + i;
-            if (kv.ring_pages) lp %= kv.ring_pages;
-            const int page = max(table[lp], 0);  // an unreserved page was flagged when the row was stored
+            if ((i & 31) == 0) {
+                int lp = p_begin + i + lane;
+                if (kv.ring_pages) lp %= kv.ring_pages;
+                // an unreserved page was flagged when the row was stored; lanes beyond the range read nothing
+                page_ids = i + lane < my_pages ? max(table[lp], 0) : 0;
+            }
+            const int page = __shfl_sync(0xffffffffu, page_ids, i & 31);
             const long long base = (((long long)page * kv.n_kv_heads + kvh) * SB_PAGE + warp * AD_KEYS_PER_WARP) * D;
             unsigned char* ks = my_pipe + (i % AD_STAGES) * 2 * SLICE;
             unsigned char* vs = ks + SLICE;

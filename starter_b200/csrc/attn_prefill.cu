@@ -68,11 +68,21 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
     const __nv_bfloat16* kbase = (const __nv_bfloat16*)kv.k;
     const __nv_bfloat16* vbase = (const __nv_bfloat16*)kv.v;
     const int* table = kv.table + (long long)slot * kv.table_width;
+    // The ids of the block's pages are fetched once, 512 at a time: a lookup in the page table costs a
+    // trip to L2, and paying it for every page would stall the copies behind it.
+    __shared__ int s_pages[512];
+    auto load_ids = [&](int base) {
+        for (int j = tid; j < 512 && base + j < n_pages; j += AP_WARPS * 32) {
+            int lp = first_page + base + j;
+            if (kv.ring_pages) lp %= kv.ring_pages;
+            s_pages[j] = max(table[lp], 0);
+        }
+    };
+    load_ids(0);
+    __syncthreads();
     auto issue = [&](int i) {
         if (i < n_pages) {
-            int lp = first_page + i;
-            if (kv.ring_pages) lp %= kv.ring_pages;
-            const int page = max(table[lp], 0);
+            const int page = s_pages[i & 511];
             const long long base = ((long long)page * kv.n_kv_heads + kvh) * SB_PAGE * D;
             unsigned char* ks = kv_s + (i & 1) * 2 * TILE;
             unsigned char* vs = ks + TILE;
@@ -97,6 +107,11 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
 
     issue(0);
     for (int i = 0; i < n_pages; ++i) {
+        if (((i + 1) & 511) == 0) {   // the next page's id is in the next batch of ids
+            __syncthreads();
+            load_ids(i + 1);
+            __syncthreads();
+        }
         issue(i + 1);
         cp_async_wait<1>();
         __syncthreads();

@@ -311,12 +311,19 @@ class Ops:
             self._sm_count = torch.cuda.get_device_properties(torch.cuda.current_device()).multi_processor_count
         return self._sm_count
 
+    def decode_resident(self, head_dim: int) -> int:
+        """Blocks of the split-key decode attention that the GPU holds at once (three per SM at head size 128)."""
+        return (3 if head_dim > 64 else 4) * self.sm_count()
+
     def decode_splits(self, n_seqs: int, n_kv_heads: int, max_pages: int, head_dim: int = 128) -> int:
-        """How many blocks share one (sequence, kv head): as many as keep all blocks resident at once
-        (three per SM at head size 128, by shared memory and registers), so there is no second wave.
+        """How many blocks share one (sequence, kv head).  Measured on a B200 at a context of 4,096: about
+        256 blocks in all is best (more blocks mean shorter shares, and a share pays fixed costs: loading
+        the queries, merging the warps, the pass through scratch memory), never more than 16 per pair.
         A function of shapes only, so that a captured graph stays valid as sequences grow."""
-        resident = (3 if head_dim > 64 else 4) * self.sm_count()
-        return max(1, min(resident // max(n_seqs * n_kv_heads, 1), max_pages, 64))
+        if os.environ.get("STARTER_B200_ATTN_SPLITS"):
+            return int(os.environ["STARTER_B200_ATTN_SPLITS"])
+        pairs = max(n_seqs * n_kv_heads, 1)
+        return max(1, min(256 // pairs, 16, max_pages, self.decode_resident(head_dim) // pairs))
 
     def _decode_scratch(self, device, n_seqs, n_heads, n_kv_heads, head_dim, n_splits):
         key = ("attn_decode", device, n_seqs, n_heads, n_kv_heads, head_dim, n_splits)
@@ -335,10 +342,11 @@ class Ops:
         out = torch.empty_like(q)
         kv = self._kv(layer_cache)
         if q.dtype == torch.bfloat16 and kv.head_dim in (64, 128):
-            if (ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and n_heads // kv.n_kv_heads <= 16 and self.decode_balanced
-                    and ctx.n_seqs <= 1024):
-                # as many blocks as the GPU holds at once (three per SM at head size 128), each with an equal share of pages
-                grid = min((3 if kv.head_dim > 64 else 4) * self.sm_count(), 512)
+            decode = ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and n_heads // kv.n_kv_heads <= 16
+            pairs = ctx.n_seqs * kv.n_kv_heads
+            if decode and self.decode_balanced and pairs > self.decode_resident(kv.head_dim) and ctx.n_seqs <= 1024:
+                # More pairs than blocks fit at once: one block per SM, each with an equal share of all pages.
+                grid = min(int(os.environ.get("STARTER_B200_ATTN_GRID", 1)) * self.sm_count(), 512)
                 key = ("attn_decode_balanced", q.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, grid)
                 buf = self._scratch.get(key)
                 if buf is None:
@@ -349,7 +357,7 @@ class Ops:
                 self._check(self.lib.sb_attn_decode_balanced(_ptr(q), _ptr(out), self._batch(ctx), kv, n_heads, scale,
                                                              int(window or 0), grid, _ptr(buf[0]), _ptr(buf[1]),
                                                              self._stream()), "attn_decode_balanced")
-            elif ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and n_heads // kv.n_kv_heads <= 16:
+            elif decode:
                 g = layer_cache.group
                 n_splits = self.decode_splits(ctx.n_seqs, kv.n_kv_heads, g.table_width, kv.head_dim)
                 partial, counters = self._decode_scratch(q.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, n_splits)

@@ -196,8 +196,10 @@ def test_decode_attention(ops, ref, monkeypatch, heads, kv_heads, head_dim, wind
     """One new token per sequence over contexts of 0 to 1500 tokens, against the torch restatement;
     in the longest sequence one far key is made to stand out."""
     dtype = torch.bfloat16
-    monkeypatch.setattr(ops, "decode_balanced", splits is None)   # None: the balanced kernel; a number: fixed splits
-    if splits is not None:
+    if splits is None:   # the balanced kernel, whatever the number of pairs
+        monkeypatch.setattr(ops, "decode_resident", lambda *a: 0)
+    else:                # the split-key kernel with a fixed number of splits
+        monkeypatch.setattr(ops, "decode_balanced", False)
         monkeypatch.setattr(ops, "decode_splits", lambda *a: splits)
     cache = Cache([KVRequest(kv_heads, head_dim, window)], n_slots=6, max_tokens=64 * 60, dtype=dtype, device="cuda",
                   max_seq_tokens=1600, max_step_tokens=64)
