@@ -48,14 +48,14 @@ __device__ __forceinline__ float silu_mul_bf16(float g, float u) {
 // take the gate rows of the block, warps 4-7 the matching up rows, and the output is swiglu(gate, up).
 // DEEP: a warp requests the next turn's weights before it multiplies the current turn (more bytes in flight
 // per warp, more registers, fewer resident blocks); worth it when few blocks share an SM.
-template <int NT, bool GATE_UP, bool DEEP>
-__global__ void __launch_bounds__(GS_WARPS * 32, DEEP ? 2 : 4)
+template <int NT, bool GATE_UP, bool DEEP, int WARPS>
+__global__ void __launch_bounds__(WARPS * 32, DEEP ? 2 : (WARPS == 8 ? 4 : 8))
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, void* __restrict__ C,
                    int M, int n_out, int K, int k_per_split, int n_splits, int out_f32, float* __restrict__ partial,
                    int* __restrict__ counters) {
     constexpr int GROUPS = GATE_UP ? 2 : 1;              // row groups the warps are divided into
-    constexpr int WPG = GS_WARPS / GROUPS;               // warps per group, sharing K among them
-    __shared__ float red[GS_WARPS][GS_ROWS][8 * NT + 1];
+    constexpr int WPG = WARPS / GROUPS;                  // warps per group, sharing K among them
+    __shared__ float red[WARPS][GS_ROWS][8 * NT + 1];
     __shared__ int s_is_last;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, c = lane & 3;
@@ -143,7 +143,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     constexpr int ELEMS = GROUPS * GS_ROWS * 8 * NT;
     const long long part_block = (long long)ELEMS;
     float* my_part = partial + ((long long)blockIdx.x * n_splits + split) * part_block;
-    for (int e = tid; e < ELEMS; e += GS_WARPS * 32) {
+    for (int e = tid; e < ELEMS; e += WARPS * 32) {
         const int grp = e / (GS_ROWS * 8 * NT), r = (e / (8 * NT)) % GS_ROWS, m = e % (8 * NT);
         float v = 0.f;
 #pragma unroll
@@ -162,7 +162,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         if (!s_is_last) return;
         __threadfence();
         const float* parts = partial + (long long)blockIdx.x * n_splits * part_block;
-        for (int e = tid; e < ELEMS; e += GS_WARPS * 32) {
+        for (int e = tid; e < ELEMS; e += WARPS * 32) {
             const int grp = e / (GS_ROWS * 8 * NT), r = (e / (8 * NT)) % GS_ROWS, m = e % (8 * NT);
             float v = 0.f;
             for (int s = 0; s < n_splits; ++s) v += __ldcg(parts + s * part_block + e);
@@ -174,7 +174,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
 
     // Epilogue: one output element per (weight row r, activation row m); consecutive threads take
     // consecutive r so that a row of C is written in runs of 16.
-    for (int e = tid; e < GS_ROWS * 8 * NT; e += GS_WARPS * 32) {
+    for (int e = tid; e < GS_ROWS * 8 * NT; e += WARPS * 32) {
         const int r = e % GS_ROWS, m = e / GS_ROWS;
         if (m >= M || n0 + r >= n_out) continue;
         float v = red[0][r][m];
@@ -200,10 +200,10 @@ long long sb_gemm_skinny_scratch_floats(int M, int n_out, int n_splits, int gate
 // A [M, K], W [n_out, K] (or [2 * n_out, K] with gate_up), C [M, n_out] bfloat16 or float.
 // Takes M <= 16 and K a multiple of 8; k_per_split a multiple of 128.
 int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int K, int n_splits, int k_per_split,
-                   int gate_up, int out_f32, int deep, float* partial, int* counters, cudaStream_t stream) {
+                   int gate_up, int out_f32, int deep, int warps, float* partial, int* counters, cudaStream_t stream) {
     if (M <= 0 || n_out <= 0) return 0;
     if (M > 16 || (K & 7) || n_splits < 1 || n_splits > 65535 || (k_per_split % GS_KWARP) ||
-        (long long)k_per_split * n_splits < K)
+        (long long)k_per_split * n_splits < K || (warps != 4 && warps != 8))
         return (int)cudaErrorInvalidValue;
     dim3 grid((n_out + GS_ROWS - 1) / GS_ROWS, n_splits);
     const __nv_bfloat16* a = (const __nv_bfloat16*)A;
@@ -211,11 +211,14 @@ int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int 
 #define SB_SKINNY(NT, GU)                                                                                              \
     do {                                                                                                               \
         if (deep)                                                                                                      \
-            sb_launch(gemm_skinny_kernel<NT, GU, true>, grid, GS_WARPS * 32, 0, stream, a, w, C, M, n_out, K, k_per_split,      \
-                                                                               n_splits, out_f32, partial, counters); \
+            sb_launch(gemm_skinny_kernel<NT, GU, true, 8>, grid, 256, 0, stream, a, w, C, M, n_out, K, k_per_split,     \
+                      n_splits, out_f32, partial, counters);                                                           \
+        else if (warps == 4)                                                                                           \
+            sb_launch(gemm_skinny_kernel<NT, GU, false, 4>, grid, 128, 0, stream, a, w, C, M, n_out, K, k_per_split,    \
+                      n_splits, out_f32, partial, counters);                                                           \
         else                                                                                                           \
-            sb_launch(gemm_skinny_kernel<NT, GU, false>, grid, GS_WARPS * 32, 0, stream, a, w, C, M, n_out, K, k_per_split,     \
-                                                                                n_splits, out_f32, partial, counters);\
+            sb_launch(gemm_skinny_kernel<NT, GU, false, 8>, grid, 256, 0, stream, a, w, C, M, n_out, K, k_per_split,    \
+                      n_splits, out_f32, partial, counters);                                                           \
     } while (0)
     if (M <= 8) {
         if (gate_up) SB_SKINNY(1, true); else SB_SKINNY(1, false);

@@ -68,7 +68,7 @@ class Ops:
             "sb_qk_rope_store": [c_int, c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_int, c_void_p, c_void_p,
                                  c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
             "sb_attention_general": [c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_void_p],
-            "sb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+            "sb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_void_p, c_void_p, c_void_p],
             "sb_gemm_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                c_void_p, c_void_p],
@@ -182,7 +182,7 @@ class Ops:
 
     SKINNY_MAX_ROWS = 8   # up to 16 run, but cuBLAS is faster from 9 rows on
     STREAM_MAX_ROWS = 64
-    STREAM_MIN_WORK = int(os.environ.get("STARTER_B200_STREAM_MIN", 40_000_000))  # elements of W below which the simpler kernels do as well
+    STREAM_MIN_WORK = int(os.environ.get("STARTER_B200_STREAM_MIN", 300_000_000))  # elements of W below which the simpler kernels do as well
 
     def kernel_status(self, device) -> torch.Tensor:
         """A status word of the kernels that are not tied to a step (bit 4: a wait inside a kernel timed out)."""
@@ -219,14 +219,25 @@ class Ops:
         return out
 
     def _takes_stream(self, M, n_out, K, gate_up) -> bool:
-        return (self.use_stream and M <= (32 if gate_up else self.STREAM_MAX_ROWS) and K % 8 == 0 and K >= 64
-                and n_out * K * (2 if gate_up else 1) >= self.STREAM_MIN_WORK)
+        """Measured on a B200 (microbench.py): per launch the TMA-fed kernel pays about 9 us before and
+        after it streams (set-up, first data, the pass through scratch for shared tiles) and then streams
+        at 6.3-6.9 TB/s; the warp-level kernel pays about 3 us and streams at 4.7 TB/s, more on very large
+        matrices, and takes at most 8 rows.  So: the output head for 9 to 64 rows, nothing smaller."""
+        return (self.use_stream and self.SKINNY_MAX_ROWS < M <= (32 if gate_up else self.STREAM_MAX_ROWS)
+                and K % 8 == 0 and K >= 64 and n_out * K * (2 if gate_up else 1) >= self.STREAM_MIN_WORK)
 
     def skinny_splits(self, blocks: int, K: int) -> int:
         """K slices per block of 16 weight rows: enough blocks for three per SM, but no slice
         shorter than 3072 columns (measured on the 4B shapes: short slices cost more in the
         pass through scratch memory than they gain in parallelism)."""
         return max(1, min(round(3 * self.sm_count() / blocks), K // 3072))
+
+    def skinny_warps(self, n_blocks: int) -> int:
+        """Warps per block.  Eight-warp blocks fit four to an SM; when the blocks number a little more than
+        that (608 for 592 places), the few left over run as a second wave on an empty GPU.  Four-warp blocks
+        fit eight to an SM, so the same blocks run at once."""
+        resident8 = 4 * self.sm_count()
+        return 4 if resident8 < n_blocks <= 2 * resident8 else 8
 
     def _skinny(self, a, w, n_out, gate_up, out_float32):
         """The weight-streaming product for a handful of rows (see gemm_skinny.cu)."""
@@ -244,8 +255,9 @@ class Ops:
             self._scratch[key] = buf
         out = torch.empty((M, n_out), dtype=torch.float32 if out_float32 else torch.bfloat16, device=a.device)
         deep = False if self.force_skinny is None else self.force_skinny[1]
+        warps = self.skinny_warps(blocks * n_splits) if self.force_skinny is None or len(self.force_skinny) < 3 else self.force_skinny[2]
         self._check(self.lib.sb_gemm_skinny(_ptr(a), _ptr(w), _ptr(out), M, n_out, K, n_splits, k_per_split, int(gate_up),
-                                            int(out_float32), int(deep), _ptr(buf[0]), _ptr(buf[1]), self._stream()),
+                                            int(out_float32), int(deep), warps, _ptr(buf[0]), _ptr(buf[1]), self._stream()),
                     "gemm_skinny")
         return out
 

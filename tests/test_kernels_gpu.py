@@ -233,13 +233,13 @@ def test_decode_attention(ops, ref, monkeypatch, heads, kv_heads, head_dim, wind
 
 
 @pytest.mark.parametrize("M", [1, 5, 8, 11, 16])
-@pytest.mark.parametrize("splits,deep", [(1, False), (3, False), (2, True)])
-def test_skinny_product_variants(ops, ref, M, splits, deep):
+@pytest.mark.parametrize("splits,deep,warps", [(1, False, 8), (3, False, 8), (2, True, 8), (1, False, 4), (2, False, 4)])
+def test_skinny_product_variants(ops, ref, M, splits, deep, warps):
     """The weight-streaming product with every row tile, K slicing and pipelining variant, with and
     without the SwiGLU epilogue, at sizes that are no multiples of its tiles."""
     dtype = torch.bfloat16
     try:
-        ops.force_skinny = (splits, deep)
+        ops.force_skinny = (splits, deep, warps)
         a, w = rand((M, 4104), dtype, 70), rand((2 * 1000, 4104), dtype, 71, 0.05)
         close(ops._skinny(a, w, 2000, False, False), ref.linear(a, w), dtype, "skinny")
         close(ops._skinny(a, w, 2000, False, True), ref.linear(a, w, out_float32=True), dtype, "skinny, 32-bit out", rel=2e-3)
