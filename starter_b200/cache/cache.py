@@ -206,6 +206,9 @@ class Cache:
                 if not 0 <= req.layer < len(requests) or self.layers[req.layer] is None:
                     raise CacheError(f"layer {i} wants to read the cache of layer {req.layer}, which has none")
                 self.layers[i] = self.layers[req.layer]
+        # Only a ring of pages limits how many tokens a sequence may bring in one forward pass.
+        self.has_rings = any(isinstance(g, KVGroup) and g.ring_pages for g in self.groups)
+        self.step_limit = self.max_step_tokens if self.has_rings else (1 << 30)
         self.lengths_host: List[int] = [0] * (self.n_slots + 1)
         self.lengths = torch.zeros(self.n_slots + 1, dtype=torch.int32, device=device)
         self._dirty_lengths = set()

@@ -75,6 +75,81 @@ __global__ void qk_rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
     }
 }
 
+
+// The common case on the tensor-core path: bfloat16, head size 128, rotary over the whole head.  One block
+// per row, a warp per head in turns, four consecutive values per lane (8-byte accesses); the rotate-half
+// partner of a lane's values sits in lane ^ 16.
+template <class W>
+__global__ void __launch_bounds__(256)
+qk_rope_store_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out, SbBatch batch, SbKV kv,
+                          int n_heads, int n_kv_heads, const W* __restrict__ q_norm_w, const W* __restrict__ k_norm_w,
+                          float eps, const __nv_bfloat16* __restrict__ cos_t, const __nv_bfloat16* __restrict__ sin_t,
+                          int* status) {
+    pdl_wait();
+    const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int width = (n_heads + 2 * n_kv_heads) * 128;
+    int slot, pos;
+    row_place(batch, row, slot, pos);
+    const int d0 = lane * 4, j0 = d0 & 63;
+    float c[4], sn[4];
+    {
+        const uint2 craw = *reinterpret_cast<const uint2*>(cos_t + (long long)pos * 64 + j0);
+        const uint2 sraw = *reinterpret_cast<const uint2*>(sin_t + (long long)pos * 64 + j0);
+        const __nv_bfloat162* ch = reinterpret_cast<const __nv_bfloat162*>(&craw);
+        const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&sraw);
+        const float2 c01 = __bfloat1622float2(ch[0]), c23 = __bfloat1622float2(ch[1]);
+        const float2 s01 = __bfloat1622float2(sh[0]), s23 = __bfloat1622float2(sh[1]);
+        c[0] = c01.x; c[1] = c01.y; c[2] = c23.x; c[3] = c23.y;
+        sn[0] = s01.x; sn[1] = s01.y; sn[2] = s23.x; sn[3] = s23.y;
+    }
+    for (int head = warp; head < n_heads + n_kv_heads; head += 8) {
+        const bool is_q = head < n_heads;
+        const __nv_bfloat16* src = qkv + (long long)row * width + (long long)head * 128;
+        const W* w = is_q ? q_norm_w : k_norm_w;
+        const uint2 raw = *reinterpret_cast<const uint2*>(src + d0);
+        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const float2 v01 = __bfloat1622float2(h2[0]), v23 = __bfloat1622float2(h2[1]);
+        float y[4] = {v01.x, v01.y, v23.x, v23.y};
+        if (w != nullptr) {
+            float ss = y[0] * y[0];
+            ss = fmaf(y[1], y[1], ss); ss = fmaf(y[2], y[2], ss); ss = fmaf(y[3], y[3], ss);
+            ss = warp_sum(ss);
+            const float rstd = 1.0f / sqrtf(ss / 128.0f + eps);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float n = rnd<__nv_bfloat16>(__fmul_rn(y[e], rstd));
+                y[e] = rnd<__nv_bfloat16>(__fmul_rn(to_f<W>(w[d0 + e]), n));
+            }
+        }
+        float o[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const float partner = __shfl_xor_sync(0xffffffffu, y[e], 16);
+            const float a = rnd<__nv_bfloat16>(__fmul_rn(y[e], c[e]));
+            const float b = rnd<__nv_bfloat16>(__fmul_rn(lane < 16 ? -partner : partner, sn[e]));
+            o[e] = __fadd_rn(a, b);
+        }
+        __nv_bfloat16* dst;
+        if (is_q) {
+            dst = q_out + (long long)row * n_heads * 128 + (long long)head * 128;
+        } else {
+            const long long off = kv_offset(kv, slot, pos, head - n_heads);
+            if (off < 0) {
+                if (lane == 0) atomicOr(status, SB_STATUS_NO_PAGE);
+                continue;
+            }
+            dst = (__nv_bfloat16*)kv.k + off;
+            *reinterpret_cast<uint2*>((__nv_bfloat16*)kv.v + off + d0) =
+                *reinterpret_cast<const uint2*>(src + (long long)n_kv_heads * 128 + d0);
+        }
+        uint2 res;
+        __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
+        r2[0] = __floats2bfloat162_rn(o[0], o[1]);
+        r2[1] = __floats2bfloat162_rn(o[2], o[3]);
+        *reinterpret_cast<uint2*>(dst + d0) = res;
+    }
+}
+
 // qkv [rows, (n_heads + 2 n_kv_heads) * D]; q_out [rows, n_heads * D]; norm weights may be null
 // (no per-head norm); cos/sin [positions, rotary_dim / 2] may be null (no rotary encoding).
 // With n_kv_heads == 0 only q is processed and nothing is stored (a layer that reads another's cache).
@@ -83,6 +158,17 @@ extern "C" int sb_qk_rope_store(int dtype, int wdtype, const void* qkv, void* q_
                                 const void* sin_t, int rotary_dim, int* status, cudaStream_t stream) {
     if (batch.n_rows <= 0) return 0;
     if (kv.head_dim > QK_MAX_D || rotary_dim > kv.head_dim || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
+    if (dtype == SB_BF16 && kv.head_dim == 128 && rotary_dim == 128 && cos_t != nullptr) {
+        if (wdtype == SB_F32)
+            sb_launch(qk_rope_store_d128_kernel<float>, batch.n_rows, 256, 0, stream, (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out,
+                      batch, kv, n_heads, n_kv_heads, (const float*)q_norm_w, (const float*)k_norm_w, eps,
+                      (const __nv_bfloat16*)cos_t, (const __nv_bfloat16*)sin_t, status);
+        else
+            sb_launch(qk_rope_store_d128_kernel<__nv_bfloat16>, batch.n_rows, 256, 0, stream, (const __nv_bfloat16*)qkv,
+                      (__nv_bfloat16*)q_out, batch, kv, n_heads, n_kv_heads, (const __nv_bfloat16*)q_norm_w,
+                      (const __nv_bfloat16*)k_norm_w, eps, (const __nv_bfloat16*)cos_t, (const __nv_bfloat16*)sin_t, status);
+        SB_LAUNCH_CHECK();
+    }
     dim3 grid(batch.n_rows, n_heads + n_kv_heads);
     if (grid.y > 65535) return (int)cudaErrorInvalidValue;
 #define SB_QK(T, W)                                                                                                    \

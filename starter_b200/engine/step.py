@@ -99,7 +99,7 @@ class Stepper:
             room = self.max_rows
             part = []
             for i, e in enumerate(entries):
-                n = min(len(e.tokens) - done[i], cache.max_step_tokens, room)
+                n = min(len(e.tokens) - done[i], cache.step_limit, room)
                 if n > 0:
                     part.append((i, done[i], n))
                     room -= n

@@ -15,7 +15,7 @@ def test_every_cutting_matches_plain(tiny_folders, name, dtype):
     folder = tiny_folders[name]
     seqs = random_tokens(TINY[name]["vocab_size"], LENGTHS, seed=11)
     ref = plain_logits(folder, seqs, dtype)
-    sess = make_session(folder, dtype, max_tokens=64 * 10, max_seqs=4, max_step_tokens=48)
+    sess = make_session(folder, dtype, max_tokens=64 * 10, max_seqs=4, max_step_tokens=48, max_rows=100)
     assert_close(run_whole(sess, seqs), ref, dtype, "alone and whole")
     assert_close(run_whole(sess, seqs[:3], together=True), ref[:3], dtype, "one ragged step")
     assert_close(run_tail_by_one(sess, seqs), ref, dtype, "tail one by one")

@@ -301,3 +301,24 @@ def test_stream_product_with_swiglu(ops, ref, shape):
     close(ops._stream_product(h, w, I, True, False), ref.linear_swiglu(h, w), dtype, "stream + swiglu")
     close(ops._stream_product(h, w, I, True, False), ref.linear_swiglu(h, w), dtype, "stream + swiglu, again")  # counters were left zero
     assert ops.read_kernel_status() == 0
+
+
+def test_rope_store_head_128_with_32_bit_norm_weights(ops, ref):
+    """The vectorised rope-and-store kernel (bfloat16, head size 128) with norm weights kept in 32-bit."""
+    dtype, heads, kv_heads, D = torch.bfloat16, 4, 2, 128
+    caches = [Cache([KVRequest(kv_heads, D)], n_slots=2, max_tokens=64 * 4, dtype=dtype, device="cuda") for _ in range(2)]
+    ang = torch.arange(200, dtype=torch.float32)[:, None] / (10000.0 ** (torch.arange(64).float() / 64))[None]
+    rotary = (ang.cos().to(dtype).cuda(), ang.sin().to(dtype).cuda(), D)
+    qn, kn = 1 + 0.1 * rand((D,), torch.float32, 100), 1 + 0.1 * rand((D,), torch.float32, 101)
+    qkv = rand((70, (heads + 2 * kv_heads) * D), dtype, 102)
+    outs = []
+    for c, o in zip(caches, (ops, ref)):
+        slot = c.alloc()
+        c.reserve(slot, 70)
+        c.flush()
+        ctx = make_ctx(c, ops, [slot], [70], dtype)
+        outs.append(o.qk_norm_rope_store(ctx, qkv, c.layers[0], heads, kv_heads, D, qn, kn, 1e-6, rotary))
+        assert int(ctx.status) == 0
+    close(outs[0], outs[1], dtype, "q", rel=8e-3)
+    close(caches[0].groups[0].k, caches[1].groups[0].k, dtype, "stored keys", rel=8e-3)
+    assert torch.equal(caches[0].groups[0].v, caches[1].groups[0].v)
