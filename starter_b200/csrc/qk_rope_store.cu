@@ -159,7 +159,7 @@ extern "C" int sb_qk_rope_store(int dtype, int wdtype, const void* qkv, void* q_
     if (batch.n_rows <= 0) return 0;
     if (kv.head_dim > QK_MAX_D || rotary_dim > kv.head_dim || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
     // (few rows, as in decode: a warp per head over many small blocks spreads over more SMs and is faster)
-    if (dtype == SB_BF16 && kv.head_dim == 128 && rotary_dim == 128 && cos_t != nullptr && batch.n_rows >= 64) {
+    if (dtype == SB_BF16 && kv.head_dim == 128 && rotary_dim == 128 && cos_t != nullptr && batch.n_rows >= 256) {
         if (wdtype == SB_F32)
             sb_launch(qk_rope_store_d128_kernel<float>, batch.n_rows, 256, 0, stream, (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out,
                       batch, kv, n_heads, n_kv_heads, (const float*)q_norm_w, (const float*)k_norm_w, eps,
