@@ -19,22 +19,18 @@
 #include "mma_utils.cuh"
 
 #define AP_WARPS 4
+#define AP_ROWS (AP_WARPS * 16)
 
-// MT: 16-row tiles per warp.  With two, a warp's fragments of a key or value page serve 32 query rows
-// (half the shared-memory reads per flop, two independent chains of products per warp); the queries
-// then come from shared memory at every step instead of living in registers.
-template <int D, int MT>
-__global__ void __launch_bounds__(AP_WARPS * 32, 2)
+template <int D>
+__global__ void __launch_bounds__(AP_WARPS * 32)
 attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, SbBatch batch, SbKV kv,
                     int n_heads, float scale_log2, int window) {
     constexpr int CH = D / 8;                   // 16-byte chunks per row
     constexpr int TILE = SB_PAGE * D * 2;       // bytes of one page of keys (or values) of one kv head
     constexpr int NT = D / 8;                   // output n-tiles
-    constexpr int WROWS = 16 * MT;              // query rows per warp
-    constexpr int ROWS = AP_WARPS * WROWS;      // query rows per block
     extern __shared__ __align__(128) unsigned char smem[];
-    unsigned char* q_s = smem;                  // [ROWS][D]
-    unsigned char* kv_s = smem + ROWS * D * 2;  // [2 stages][K tile | V tile]
+    unsigned char* q_s = smem;                  // [64][D]
+    unsigned char* kv_s = smem + AP_ROWS * D * 2;  // [2 stages][K tile | V tile]
     pdl_wait();
 
     const int seq = blockIdx.z, kvh = blockIdx.y;
@@ -46,16 +42,16 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
     const int start = batch.lengths[slot];                      // position of the sequence's first new row
     const int total = q_len * G;                                // (position, head) rows of this sequence and kv head
     const int tile = gridDim.x - 1 - blockIdx.x;                // latest rows (most keys) first
-    const int t0 = tile * ROWS;
+    const int t0 = tile * AP_ROWS;
     if (t0 >= total) return;
-    const int t_last = min(t0 + ROWS, total) - 1;
+    const int t_last = min(t0 + AP_ROWS, total) - 1;
     const int pos_min = start + t0 / G, pos_max = start + t_last / G;
     const int lo_min = window > 0 ? max(0, pos_min - window + 1) : 0;
     const int first_page = lo_min / SB_PAGE, last_page = pos_max / SB_PAGE;
     const int n_pages = last_page - first_page + 1;
 
-    // Query rows into shared memory (zero beyond the sequence's rows).
-    for (int i = tid; i < ROWS * CH; i += AP_WARPS * 32) {
+    // Query rows into shared memory (zero beyond the sequence's rows), then into fragments.
+    for (int i = tid; i < AP_ROWS * CH; i += AP_WARPS * 32) {
         const int r = i / CH, c = i % CH;
         const int t = t0 + r;
         uint4 v = make_uint4(0u, 0u, 0u, 0u);
@@ -63,6 +59,11 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
             v = *reinterpret_cast<const uint4*>(q + ((long long)(row0 + t / G) * n_heads + kvh * G + t % G) * D + c * 8);
         *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
     }
+    __syncthreads();
+    unsigned int qf[D / 16][4];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks)
+        ldmatrix_x4(qf[ks], q_s + tile_off<D>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
 
     const __nv_bfloat16* kbase = (const __nv_bfloat16*)kv.k;
     const __nv_bfloat16* vbase = (const __nv_bfloat16*)kv.v;
@@ -79,12 +80,6 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
     };
     load_ids(0);
     __syncthreads();
-    unsigned int q_regs[MT == 1 ? D / 16 : 1][4];
-    if (MT == 1) {
-#pragma unroll
-        for (int ks = 0; ks < D / 16; ++ks)
-            ldmatrix_x4(q_regs[ks], q_s + tile_off<D>(warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
-    }
     auto issue = [&](int i) {
         if (i < n_pages) {
             const int page = s_pages[i & 511];
@@ -100,26 +95,15 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
         cp_async_commit();
     };
 
-    // This thread's rows (two per 16-row tile): their positions and first visible keys.
-    int pos_r[MT][2], lo_r[MT][2], tr[MT][2];
-#pragma unroll
-    for (int t = 0; t < MT; ++t)
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            tr[t][h] = t0 + warp * WROWS + t * 16 + (lane >> 2) + 8 * h;
-            pos_r[t][h] = tr[t][h] < total ? start + tr[t][h] / G : -1;
-            lo_r[t][h] = window > 0 ? max(0, pos_r[t][h] - window + 1) : 0;
-        }
+    // This thread's two rows: their positions and first visible keys.
+    const int tr0 = t0 + warp * 16 + (lane >> 2), tr1 = tr0 + 8;
+    const int p0 = tr0 < total ? start + tr0 / G : -1, p1 = tr1 < total ? start + tr1 / G : -1;
+    const int lo0 = window > 0 ? max(0, p0 - window + 1) : 0, lo1 = window > 0 ? max(0, p1 - window + 1) : 0;
 
-    float m[MT][2], l[MT][2];
-    float acc[MT][NT][4];
+    float m[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
+    float acc[NT][4];
 #pragma unroll
-    for (int t = 0; t < MT; ++t) {
-        m[t][0] = m[t][1] = -INFINITY;
-        l[t][0] = l[t][1] = 0.f;
-#pragma unroll
-        for (int j = 0; j < NT; ++j) acc[t][j][0] = acc[t][j][1] = acc[t][j][2] = acc[t][j][3] = 0.f;
-    }
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
     issue(0);
     for (int i = 0; i < n_pages; ++i) {
@@ -135,99 +119,74 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
         const unsigned char* vs = ks + TILE;
         const int key0 = (first_page + i) * SB_PAGE;
         // A warp whose rows all lie before this page, or whose windows all lie after it, has nothing here.
-        const int w_first = t0 + warp * WROWS, w_last = min(w_first + WROWS - 1, total - 1);
+        const int w_first = t0 + warp * 16, w_last = min(w_first + 15, total - 1);
         const bool warp_has = w_first < total && key0 <= start + w_last / G &&
                               (window <= 0 || key0 + SB_PAGE - 1 >= start + w_first / G - window + 1);
         if (warp_has) {
-            float s[MT][SB_PAGE / 8][4];
+            float s[SB_PAGE / 8][4];
 #pragma unroll
-            for (int t = 0; t < MT; ++t)
-#pragma unroll
-                for (int nt = 0; nt < SB_PAGE / 8; ++nt) s[t][nt][0] = s[t][nt][1] = s[t][nt][2] = s[t][nt][3] = 0.f;
+            for (int nt = 0; nt < SB_PAGE / 8; ++nt) s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.f;
 #pragma unroll
             for (int kk = 0; kk < D / 16; ++kk) {
-                unsigned int qf[MT][4];
-#pragma unroll
-                for (int t = 0; t < MT; ++t) {
-                    if (MT == 1) {
-                        qf[t][0] = q_regs[kk][0]; qf[t][1] = q_regs[kk][1]; qf[t][2] = q_regs[kk][2]; qf[t][3] = q_regs[kk][3];
-                    } else {
-                        ldmatrix_x4(qf[t], q_s + tile_off<D>(warp * WROWS + t * 16 + (lane & 7) + ((lane >> 3) & 1) * 8,
-                                                             kk * 2 + (lane >> 4)));
-                    }
-                }
 #pragma unroll
                 for (int np = 0; np < SB_PAGE / 16; ++np) {
                     unsigned int b[4];
                     ldmatrix_x4(b, ks + tile_off<D>(np * 16 + (lane & 7) + (lane >> 4) * 8, kk * 2 + ((lane >> 3) & 1)));
-#pragma unroll
-                    for (int t = 0; t < MT; ++t) {
-                        mma_bf16(s[t][2 * np], qf[t], b[0], b[1]);
-                        mma_bf16(s[t][2 * np + 1], qf[t], b[2], b[3]);
-                    }
+                    mma_bf16(s[2 * np], qf[kk], b[0], b[1]);
+                    mma_bf16(s[2 * np + 1], qf[kk], b[2], b[3]);
                 }
             }
-            float alpha[MT][2];
+            float mx[2] = {-INFINITY, -INFINITY};
 #pragma unroll
-            for (int t = 0; t < MT; ++t) {
-                float mx[2] = {-INFINITY, -INFINITY};
+            for (int nt = 0; nt < SB_PAGE / 8; ++nt) {
+                const int n = key0 + nt * 8 + (lane & 3) * 2;
+                s[nt][0] = (n <= p0 && n >= lo0) ? s[nt][0] * scale_log2 : -INFINITY;
+                s[nt][1] = (n + 1 <= p0 && n + 1 >= lo0) ? s[nt][1] * scale_log2 : -INFINITY;
+                s[nt][2] = (n <= p1 && n >= lo1) ? s[nt][2] * scale_log2 : -INFINITY;
+                s[nt][3] = (n + 1 <= p1 && n + 1 >= lo1) ? s[nt][3] * scale_log2 : -INFINITY;
+                mx[0] = fmaxf(mx[0], fmaxf(s[nt][0], s[nt][1]));
+                mx[1] = fmaxf(mx[1], fmaxf(s[nt][2], s[nt][3]));
+            }
+            float alpha[2], m_safe[2];
 #pragma unroll
-                for (int nt = 0; nt < SB_PAGE / 8; ++nt) {
-                    const int n = key0 + nt * 8 + (lane & 3) * 2;
-                    s[t][nt][0] = (n <= pos_r[t][0] && n >= lo_r[t][0]) ? s[t][nt][0] * scale_log2 : -INFINITY;
-                    s[t][nt][1] = (n + 1 <= pos_r[t][0] && n + 1 >= lo_r[t][0]) ? s[t][nt][1] * scale_log2 : -INFINITY;
-                    s[t][nt][2] = (n <= pos_r[t][1] && n >= lo_r[t][1]) ? s[t][nt][2] * scale_log2 : -INFINITY;
-                    s[t][nt][3] = (n + 1 <= pos_r[t][1] && n + 1 >= lo_r[t][1]) ? s[t][nt][3] * scale_log2 : -INFINITY;
-                    mx[0] = fmaxf(mx[0], fmaxf(s[t][nt][0], s[t][nt][1]));
-                    mx[1] = fmaxf(mx[1], fmaxf(s[t][nt][2], s[t][nt][3]));
-                }
-                float m_safe[2];
+            for (int h = 0; h < 2; ++h) {
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+                mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+                const float m_new = fmaxf(m[h], mx[h]);
+                m_safe[h] = m_new == -INFINITY ? 0.f : m_new;
+                alpha[h] = exp2f(m[h] - m_safe[h]);
+                m[h] = m_new;
+            }
+            float sum[2] = {0.f, 0.f};
 #pragma unroll
-                for (int h = 0; h < 2; ++h) {
-                    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-                    mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-                    const float m_new = fmaxf(m[t][h], mx[h]);
-                    m_safe[h] = m_new == -INFINITY ? 0.f : m_new;
-                    alpha[t][h] = exp2f(m[t][h] - m_safe[h]);
-                    m[t][h] = m_new;
-                }
-                float sum[2] = {0.f, 0.f};
+            for (int nt = 0; nt < SB_PAGE / 8; ++nt) {
+                s[nt][0] = exp2f(s[nt][0] - m_safe[0]);
+                s[nt][1] = exp2f(s[nt][1] - m_safe[0]);
+                s[nt][2] = exp2f(s[nt][2] - m_safe[1]);
+                s[nt][3] = exp2f(s[nt][3] - m_safe[1]);
+                sum[0] += s[nt][0] + s[nt][1];
+                sum[1] += s[nt][2] + s[nt][3];
+            }
+            l[0] = l[0] * alpha[0] + sum[0];
+            l[1] = l[1] * alpha[1] + sum[1];
 #pragma unroll
-                for (int nt = 0; nt < SB_PAGE / 8; ++nt) {
-                    s[t][nt][0] = exp2f(s[t][nt][0] - m_safe[0]);
-                    s[t][nt][1] = exp2f(s[t][nt][1] - m_safe[0]);
-                    s[t][nt][2] = exp2f(s[t][nt][2] - m_safe[1]);
-                    s[t][nt][3] = exp2f(s[t][nt][3] - m_safe[1]);
-                    sum[0] += s[t][nt][0] + s[t][nt][1];
-                    sum[1] += s[t][nt][2] + s[t][nt][3];
-                }
-                l[t][0] = l[t][0] * alpha[t][0] + sum[0];
-                l[t][1] = l[t][1] * alpha[t][1] + sum[1];
-#pragma unroll
-                for (int j = 0; j < NT; ++j) {
-                    acc[t][j][0] *= alpha[t][0]; acc[t][j][1] *= alpha[t][0];
-                    acc[t][j][2] *= alpha[t][1]; acc[t][j][3] *= alpha[t][1];
-                }
+            for (int j = 0; j < NT; ++j) {
+                acc[j][0] *= alpha[0]; acc[j][1] *= alpha[0];
+                acc[j][2] *= alpha[1]; acc[j][3] *= alpha[1];
             }
 #pragma unroll
             for (int kb = 0; kb < SB_PAGE / 16; ++kb) {   // 16 keys at a time
-                unsigned int pf[MT][4];
-#pragma unroll
-                for (int t = 0; t < MT; ++t) {
-                    pf[t][0] = pack_bf16(s[t][2 * kb][0], s[t][2 * kb][1]);
-                    pf[t][1] = pack_bf16(s[t][2 * kb][2], s[t][2 * kb][3]);
-                    pf[t][2] = pack_bf16(s[t][2 * kb + 1][0], s[t][2 * kb + 1][1]);
-                    pf[t][3] = pack_bf16(s[t][2 * kb + 1][2], s[t][2 * kb + 1][3]);
-                }
+                unsigned int pf[4];
+                pf[0] = pack_bf16(s[2 * kb][0], s[2 * kb][1]);
+                pf[1] = pack_bf16(s[2 * kb][2], s[2 * kb][3]);
+                pf[2] = pack_bf16(s[2 * kb + 1][0], s[2 * kb + 1][1]);
+                pf[3] = pack_bf16(s[2 * kb + 1][2], s[2 * kb + 1][3]);
 #pragma unroll
                 for (int j = 0; j < NT; j += 2) {
                     unsigned int b[4];
                     ldmatrix_x4_trans(b, vs + tile_off<D>(kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, j + (lane >> 4)));
-#pragma unroll
-                    for (int t = 0; t < MT; ++t) {
-                        mma_bf16(acc[t][j], pf[t], b[0], b[1]);
-                        mma_bf16(acc[t][j + 1], pf[t], b[2], b[3]);
-                    }
+                    mma_bf16(acc[j], pf, b[0], b[1]);
+                    mma_bf16(acc[j + 1], pf, b[2], b[3]);
                 }
             }
         }
@@ -236,41 +195,43 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
     cp_async_wait<0>();
     pdl_launch_dependents();
 
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
+        l[h] += __shfl_xor_sync(0xffffffffu, l[h], 2);
+    }
     const int cc = (lane & 3) * 2;
+    if (tr0 < total) {
+        const float inv = 1.0f / l[0];
+        __nv_bfloat16* o = out + ((long long)(row0 + tr0 / G) * n_heads + kvh * G + tr0 % G) * D;
 #pragma unroll
-    for (int t = 0; t < MT; ++t)
+        for (int j = 0; j < NT; ++j)
+            *reinterpret_cast<__nv_bfloat162*>(o + j * 8 + cc) = __floats2bfloat162_rn(acc[j][0] * inv, acc[j][1] * inv);
+    }
+    if (tr1 < total) {
+        const float inv = 1.0f / l[1];
+        __nv_bfloat16* o = out + ((long long)(row0 + tr1 / G) * n_heads + kvh * G + tr1 % G) * D;
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            float lsum = l[t][h];
-            lsum += __shfl_xor_sync(0xffffffffu, lsum, 1);
-            lsum += __shfl_xor_sync(0xffffffffu, lsum, 2);
-            if (tr[t][h] < total) {
-                const float inv = 1.0f / lsum;
-                __nv_bfloat16* o = out + ((long long)(row0 + tr[t][h] / G) * n_heads + kvh * G + tr[t][h] % G) * D;
-#pragma unroll
-                for (int j = 0; j < NT; ++j)
-                    *reinterpret_cast<__nv_bfloat162*>(o + j * 8 + cc) =
-                        __floats2bfloat162_rn(acc[t][j][2 * h] * inv, acc[t][j][2 * h + 1] * inv);
-            }
-        }
+        for (int j = 0; j < NT; ++j)
+            *reinterpret_cast<__nv_bfloat162*>(o + j * 8 + cc) = __floats2bfloat162_rn(acc[j][2] * inv, acc[j][3] * inv);
+    }
 }
 
-template <int D, int MT> static int launch_prefill(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale,
-                                                   int window, int max_q_len, cudaStream_t stream) {
-    constexpr int ROWS = AP_WARPS * 16 * MT;
-    const int smem = ROWS * D * 2 + 2 * 2 * SB_PAGE * D * 2;
+template <int D> static int launch_prefill(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale,
+                                           int window, int max_q_len, cudaStream_t stream) {
+    const int smem = AP_ROWS * D * 2 + 2 * 2 * SB_PAGE * D * 2;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D, MT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const int G = n_heads / kv.n_kv_heads;
-    const long long tiles = ((long long)max_q_len * G + ROWS - 1) / ROWS;
+    const long long tiles = ((long long)max_q_len * G + AP_ROWS - 1) / AP_ROWS;
     if (tiles > 2147483647LL || kv.n_kv_heads > 65535 || batch.n_seqs > 65535) return (int)cudaErrorInvalidValue;
     dim3 grid((unsigned int)tiles, kv.n_kv_heads, batch.n_seqs);
-    sb_launch(attn_prefill_kernel<D, MT>, grid, AP_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv,
-              n_heads, scale * 1.4426950408889634f, window);
+    sb_launch(attn_prefill_kernel<D>, grid, AP_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv,
+                                                                  n_heads, scale * 1.4426950408889634f, window);
     return (int)cudaGetLastError();
 }
 
@@ -280,13 +241,7 @@ extern "C" int sb_attn_prefill(const void* q, void* out, SbBatch batch, SbKV kv,
                                int max_q_len, cudaStream_t stream) {
     if (batch.n_rows <= 0) return 0;
     if (n_heads % kv.n_kv_heads || max_q_len < 1) return (int)cudaErrorInvalidValue;
-    // 32 rows per warp when the longest sequence fills at least two such blocks, else 16
-    const bool wide = (long long)max_q_len * (n_heads / kv.n_kv_heads) >= 256;
-    if (kv.head_dim == 128)
-        return wide ? launch_prefill<128, 2>(q, out, batch, kv, n_heads, scale, window, max_q_len, stream)
-                    : launch_prefill<128, 1>(q, out, batch, kv, n_heads, scale, window, max_q_len, stream);
-    if (kv.head_dim == 64)
-        return wide ? launch_prefill<64, 2>(q, out, batch, kv, n_heads, scale, window, max_q_len, stream)
-                    : launch_prefill<64, 1>(q, out, batch, kv, n_heads, scale, window, max_q_len, stream);
+    if (kv.head_dim == 128) return launch_prefill<128>(q, out, batch, kv, n_heads, scale, window, max_q_len, stream);
+    if (kv.head_dim == 64) return launch_prefill<64>(q, out, batch, kv, n_heads, scale, window, max_q_len, stream);
     return (int)cudaErrorInvalidValue;
 }
