@@ -1,0 +1,369 @@
+// Prefill attention on the Blackwell tensor cores: S = Q K^T and O = P V by tcgen05.mma, S and the
+// page's O in tensor memory, keys and values brought in by TMA.  Head size 128, bfloat16.
+//
+// Same meaning and numerics as attn_prefill.cu (reference: engine/model.py:268-274 for the call,
+// engine/kernels/attention.py:9-11,75 for the numerics and the mask): scores, maximum, exp and sum in
+// 32-bit, probabilities rounded to bfloat16 before they meet V, 32-bit accumulation, one division.
+//
+// Layout of the work.  As in attn_prefill.cu the query rows of one sequence and one key/value head are
+// the pairs (new position, query head of the group), position-major; a block takes 128 of them, one per
+// thread and per lane of tensor memory.  Per key page (64 keys, one cache page):
+//   thread 0 issues  S[128 x 64] = Q[128 x 128] K^T          (8 tcgen05.mma of K = 16, both operands K-major)
+//   every thread reads its row of S from tensor memory, masks, updates its running maximum and sum,
+//   and writes its row of P (bfloat16) into shared memory in the layout the tensor core reads
+//   thread 0 issues  O_page[128 x 128] = P[128 x 64] V       (4 tcgen05.mma; V as it lies in the cache,
+//                                                             [key][d], is the MN-major form of that operand)
+//   every thread reads its row of O_page and folds it into its 128 accumulators: acc = acc * alpha + O_page.
+// Keys and values of the next page arrive by TMA while the current page is worked on.  Two blocks share an
+// SM (112 KB of shared memory and 256 columns of tensor memory each), so one block's softmax overlaps the
+// other's products.  Every wait on an mbarrier is bounded; on a time-out the block raises
+// SB_STATUS_TIMEOUT, leaves its loop at the next block-wide barrier and frees its tensor memory.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+#define SB_STATUS_TIMEOUT 4
+#define PT_ROWS 128
+#define PT_D 128
+#define PT_WAIT_LIMIT (1ll << 31)
+#define PT_IDS 128
+
+namespace {
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
+// Waits for the phase of the given parity, for a bounded time; on a time-out raises the flags and returns.
+__device__ __forceinline__ void mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
+    if (mbar_try_wait(bar, parity)) return;
+    const long long t0 = clock64();
+    while (!mbar_try_wait(bar, parity)) {
+        if (*abort_flag) return;
+        if (clock64() - t0 > PT_WAIT_LIMIT) {
+            *abort_flag = 1;
+            atomicOr(status, SB_STATUS_TIMEOUT);
+            return;
+        }
+    }
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 consecutive 32-bit columns of this warp's 32 lanes of tensor memory.
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+                   "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+                   "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory descriptors (sm_100 version, 128-byte swizzle).
+// K-major tile [rows][64 elements]: rows 128 bytes apart, groups of eight rows 1024 bytes apart.
+__device__ __forceinline__ uint64_t desc_k_major(const void* tile) {
+    return (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// MN-major operand stored as [k rows][64 elements of MN] per block of 64: k rows 128 bytes apart, groups of
+// eight k rows 1024 bytes apart (stride offset), the next 64 elements of MN `mn_block_bytes` further (leading offset).
+__device__ __forceinline__ uint64_t desc_mn_major(const void* tile, uint32_t mn_block_bytes) {
+    return (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4) | ((uint64_t)(mn_block_bytes >> 4) << 16) |
+           ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// bfloat16 x bfloat16 -> float, M = 128; b_mn_major: operand B is MN-major.
+__device__ __forceinline__ uint32_t idesc(int n, int b_mn_major) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)b_mn_major << 16) | ((uint32_t)(n >> 3) << 17) |
+           ((uint32_t)(PT_ROWS >> 4) << 24);
+}
+
+}  // namespace
+
+__global__ void __launch_bounds__(128, 2)
+attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                       const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, SbBatch batch, SbKV kv,
+                       int n_heads, float scale_log2, int window, int* status) {
+    constexpr int Q_ATOM = PT_ROWS * 128;          // bytes of a [128 rows][64 d] block of Q
+    constexpr int KV_ATOM = SB_PAGE * 128;         // bytes of a [64 keys][64 d] block of K or V
+    constexpr int STAGE = 2 * KV_ATOM;             // one page of keys (or values) of one kv head
+    extern __shared__ __align__(1024) unsigned char smem[];   // no static shared memory: the window starts 1024-aligned
+    unsigned char* q_s = smem;                     // 2 blocks of [128][64]
+    unsigned char* k_s = q_s + 2 * Q_ATOM;         // [2 stages][2 blocks of [64][64]]
+    unsigned char* v_s = k_s + 2 * STAGE;          // [2 stages][2 blocks of [64][64]]
+    unsigned char* p_s = v_s + 2 * STAGE;          // [128][64] probabilities
+    uint64_t* bars = (uint64_t*)(p_s + PT_ROWS * 128);
+    uint64_t* kv_full = bars;                      // [2]
+    uint64_t* s_done = bars + 2;
+    uint64_t* o_done = bars + 3;
+    uint32_t* tmem_slot = (uint32_t*)(bars + 4);
+    volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
+    int* s_pages = (int*)(tmem_slot + 4);          // [PT_IDS] ids of the block's next pages
+    pdl_wait();
+    if ((smem_u32(smem) & 1023u) != 0) {           // the swizzled tiles need it; never seen, but never assumed
+        if (threadIdx.x == 0) atomicOr(status, SB_STATUS_TIMEOUT);
+        return;
+    }
+
+    const int seq = blockIdx.z, kvh = blockIdx.y;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int G = n_heads / kv.n_kv_heads;
+    const int slot = batch.seq_slot[seq];
+    const int row0 = batch.cu_q[seq];
+    const int q_len = batch.cu_q[seq + 1] - row0;
+    const int start = batch.lengths[slot];
+    const int total = q_len * G;
+    const int tile = gridDim.x - 1 - blockIdx.x;   // latest rows (most keys) first
+    const int t0 = tile * PT_ROWS;
+    if (t0 >= total) return;
+    const int t_last = min(t0 + PT_ROWS, total) - 1;
+    const int pos_min = start + t0 / G, pos_max = start + t_last / G;
+    const int lo_min = window > 0 ? max(0, pos_min - window + 1) : 0;
+    const int first_page = lo_min / SB_PAGE, last_page = pos_max / SB_PAGE;
+    const int n_pages = last_page - first_page + 1;
+
+    if (tid == 0) {
+        mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1); mbar_init(s_done, 1); mbar_init(o_done, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // This thread's query row into shared memory, in the swizzled K-major layout the tensor core reads.
+    const int t = t0 + tid;
+    const int pos = t < total ? start + t / G : -1;
+    const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    {
+        const __nv_bfloat16* src = q + ((long long)(row0 + (t < total ? t / G : 0)) * n_heads + kvh * G + (t < total ? t % G : 0)) * PT_D;
+#pragma unroll
+        for (int c = 0; c < 16; ++c) {
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (t < total) v = *reinterpret_cast<const uint4*>(src + c * 8);
+            *reinterpret_cast<uint4*>(q_s + (c >> 3) * Q_ATOM + tid * 128 + (((c & 7) ^ (tid & 7)) << 4)) = v;
+        }
+    }
+    const int* table = kv.table + (long long)slot * kv.table_width;
+    auto load_ids = [&](int base) {
+        for (int j = tid; j < PT_IDS && base + j < n_pages; j += 128) {
+            int lp = first_page + base + j;
+            if (kv.ring_pages) lp %= kv.ring_pages;
+            s_pages[j] = max(table[lp], 0);
+        }
+    };
+    load_ids(0);
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // Q was written by ordinary stores
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 lanes
+    const uint32_t idesc_s = idesc(SB_PAGE, 0), idesc_o = idesc(PT_D, 1);
+
+    auto issue_page = [&](int i) {   // thread 0: keys and values of the block's i-th page into stage i & 1
+        const int page = s_pages[i & (PT_IDS - 1)];
+        const int y = (page * kv.n_kv_heads + kvh) * SB_PAGE;
+        uint64_t* bar = &kv_full[i & 1];
+        mbar_expect_tx(bar, 2 * STAGE);
+        tma_load_2d(k_s + (i & 1) * STAGE, &map_k, 0, y, bar);
+        tma_load_2d(k_s + (i & 1) * STAGE + KV_ATOM, &map_k, 64, y, bar);
+        tma_load_2d(v_s + (i & 1) * STAGE, &map_v, 0, y, bar);
+        tma_load_2d(v_s + (i & 1) * STAGE + KV_ATOM, &map_v, 64, y, bar);
+    };
+
+    float m_run = -INFINITY, l_run = 0.f;
+    float acc[PT_D];
+#pragma unroll
+    for (int d = 0; d < PT_D; ++d) acc[d] = 0.f;
+
+    if (tid == 0) issue_page(0);
+    uint32_t kv_phase[2] = {0, 0}, s_phase = 0, o_phase = 0;
+    for (int i = 0; i < n_pages; ++i) {
+        if (((i + 1) & (PT_IDS - 1)) == 0) {   // the next page's id is in the next batch of ids
+            __syncthreads();
+            load_ids(i + 1);
+            __syncthreads();
+        }
+        const int stage = i & 1;
+        if (tid == 0) {
+            if (i + 1 < n_pages) issue_page(i + 1);   // its stage was last read by the products of page i - 1, which are done
+            mbar_wait(&kv_full[stage], kv_phase[stage], abort_flag, status);
+            tc_fence_after();
+            const unsigned char* kt = k_s + stage * STAGE;
+#pragma unroll
+            for (int ks = 0; ks < PT_D / 16; ++ks)
+                tc_mma(tmem, desc_k_major(q_s + (ks >> 2) * Q_ATOM) + 2 * (ks & 3), desc_k_major(kt + (ks >> 2) * KV_ATOM) + 2 * (ks & 3),
+                       idesc_s, ks > 0 ? 1u : 0u);
+            tc_commit(s_done);
+        }
+        kv_phase[stage] ^= 1;
+        mbar_wait(s_done, s_phase, abort_flag, status);
+        s_phase ^= 1;
+        tc_fence_after();
+
+        // This thread's row of scores: mask, running maximum and sum, probabilities to shared memory.
+        const int key0 = (first_page + i) * SB_PAGE;
+        float s[SB_PAGE];
+        tc_ld32(tmem_row, s);
+        tc_ld32(tmem_row + 32, s + 32);
+        float mx = -INFINITY;
+#pragma unroll
+        for (int c = 0; c < SB_PAGE; ++c) {
+            const int n = key0 + c;
+            s[c] = (n <= pos && n >= lo) ? s[c] * scale_log2 : -INFINITY;
+            mx = fmaxf(mx, s[c]);
+        }
+        const float m_new = fmaxf(m_run, mx);
+        const float m_safe = m_new == -INFINITY ? 0.f : m_new;
+        const float alpha = exp2f(m_run - m_safe);
+        m_run = m_new;
+        float sum = 0.f;
+#pragma unroll
+        for (int c = 0; c < SB_PAGE; c += 8) {
+            uint4 packed;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float p0 = exp2f(s[c + 2 * e] - m_safe), p1 = exp2f(s[c + 2 * e + 1] - m_safe);
+                sum += p0 + p1;
+                h2[e] = __floats2bfloat162_rn(p0, p1);
+            }
+            *reinterpret_cast<uint4*>(p_s + tid * 128 + ((((c >> 3) ^ (tid & 7))) << 4)) = packed;
+        }
+        l_run = l_run * alpha + sum;
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P was written by ordinary stores
+        tc_fence_before();
+        __syncthreads();
+        if (*abort_flag) break;
+        if (tid == 0) {
+            tc_fence_after();
+            const unsigned char* vt = v_s + stage * STAGE;
+#pragma unroll
+            for (int ks = 0; ks < SB_PAGE / 16; ++ks)   // 16 keys per step: 32 bytes along P's rows, two groups of eight key rows of V
+                tc_mma(tmem + SB_PAGE, desc_k_major(p_s) + 2 * ks, desc_mn_major(vt + ks * 2048, KV_ATOM), idesc_o, ks > 0 ? 1u : 0u);
+            tc_commit(o_done);
+        }
+        mbar_wait(o_done, o_phase, abort_flag, status);
+        o_phase ^= 1;
+        tc_fence_after();
+#pragma unroll
+        for (int d0 = 0; d0 < PT_D; d0 += 32) {
+            float o[32];
+            tc_ld32(tmem_row + SB_PAGE + d0, o);
+#pragma unroll
+            for (int d = 0; d < 32; ++d) acc[d0 + d] = fmaf(acc[d0 + d], alpha, o[d]);
+        }
+        tc_fence_before();
+        __syncthreads();   // everyone has read S and O_page: the next page may overwrite them
+        if (*abort_flag) break;
+    }
+    pdl_launch_dependents();
+    if (*abort_flag && tid == 0) {   // leaving early: give the copy in flight a bounded time to land
+        const long long t_abort = clock64();
+        while (clock64() - t_abort < (1ll << 22)) {}
+    }
+    if (t < total && !*abort_flag) {
+        const float inv = 1.0f / l_run;
+        __nv_bfloat16* o = out + ((long long)(row0 + t / G) * n_heads + kvh * G + t % G) * PT_D;
+#pragma unroll
+        for (int d = 0; d < PT_D; d += 8) {
+            uint4 packed;
+            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(acc[d + 2 * e] * inv, acc[d + 2 * e + 1] * inv);
+            *reinterpret_cast<uint4*>(o + d) = packed;
+        }
+    }
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
+}
+
+// ---- host side ----------------------------------------------------------------------------------
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult qr;
+        if (cudaGetDriverEntryPointByVersion("cuTensorMapEncodeTiled", &p, 12000, cudaEnableDefault, &qr) == cudaSuccess &&
+            qr == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+// The pages of one layer's keys (or values) as a matrix [pages * kv_heads * 64 rows][128 columns] of
+// bfloat16, read in boxes of 64 rows x 64 columns with the 128-byte swizzle.
+static int make_page_map(CUtensorMap* map, const void* ptr, long long rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return (int)cudaErrorNotSupported;
+    cuuint64_t dims[2] = {PT_D, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {PT_D * 2};
+    cuuint32_t box[2] = {64, SB_PAGE};
+    cuuint32_t elem[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(ptr), dims, strides, box, elem,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : (int)cudaErrorInvalidValue;
+}
+
+// q, out [rows, n_heads * 128] bfloat16; n_pages: pages in the layer's pool (the null page included);
+// max_q_len bounds the rows any sequence brings.  Head size 128 only.
+extern "C" int sb_attn_prefill_tc(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale, int window,
+                                  int max_q_len, int n_pages, int* status, cudaStream_t stream) {
+    if (batch.n_rows <= 0) return 0;
+    if (kv.head_dim != PT_D || n_heads % kv.n_kv_heads || max_q_len < 1 || n_pages < 1) return (int)cudaErrorInvalidValue;
+    const int smem = 2 * PT_ROWS * 128 + 4 * 2 * SB_PAGE * 128 + PT_ROWS * 128 + 64 + PT_IDS * 4;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    CUtensorMap mk, mv;
+    const long long rows = (long long)n_pages * kv.n_kv_heads * SB_PAGE;
+    int e = make_page_map(&mk, kv.k, rows);
+    if (e) return e;
+    e = make_page_map(&mv, kv.v, rows);
+    if (e) return e;
+    const int G = n_heads / kv.n_kv_heads;
+    const long long tiles = ((long long)max_q_len * G + PT_ROWS - 1) / PT_ROWS;
+    if (tiles > 2147483647LL || kv.n_kv_heads > 65535 || batch.n_seqs > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid((unsigned int)tiles, kv.n_kv_heads, batch.n_seqs);
+    sb_launch(attn_prefill_tc_kernel, grid, 128, smem, stream, mk, mv, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv, n_heads,
+              scale * 1.4426950408889634f, window, status);
+    return (int)cudaGetLastError();
+}

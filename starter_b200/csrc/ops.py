@@ -73,6 +73,7 @@ class Ops:
             "sb_gemm_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                c_void_p, c_void_p],
             "sb_gemm_stream_plan": [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int)],
+            "sb_attn_prefill_tc": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_int, c_void_p, c_void_p],
             "sb_attn_prefill": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p],
             "sb_attn_decode_balanced": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
                                         c_void_p],
@@ -93,6 +94,7 @@ class Ops:
         self.use_stream = os.environ.get("STARTER_B200_STREAM", "1") != "0"  # the TMA + tcgen05 product for decode
         self._kernel_status = None
         self.decode_balanced = os.environ.get("STARTER_B200_ATTN", "balanced") != "split"
+        self.prefill_tensor_memory = os.environ.get("STARTER_B200_PREFILL", "tc") != "mma"
 
     # ---- plumbing -----------------------------------------------------------------------
 
@@ -376,6 +378,12 @@ class Ops:
                 self._check(self.lib.sb_attn_decode(_ptr(q), _ptr(out), self._batch(ctx), kv, n_heads, scale,
                                                     int(window or 0), n_splits, _ptr(partial), _ptr(counters),
                                                     self._stream()), "attn_decode")
+            elif (self.prefill_tensor_memory and kv.head_dim == 128
+                  and ctx.max_q_len * (n_heads // kv.n_kv_heads) >= 128):
+                # long pieces at head size 128: the tcgen05 kernel (S and O in tensor memory, TMA for keys and values)
+                self._check(self.lib.sb_attn_prefill_tc(_ptr(q), _ptr(out), self._batch(ctx), kv, n_heads, scale,
+                                                        int(window or 0), ctx.max_q_len, layer_cache.group.pool_pages + 1,
+                                                        _ptr(self.kernel_status(q.device)), self._stream()), "attn_prefill_tc")
             else:
                 self._check(self.lib.sb_attn_prefill(_ptr(q), _ptr(out), self._batch(ctx), kv, n_heads, scale,
                                                      int(window or 0), ctx.max_q_len, self._stream()), "attn_prefill")
