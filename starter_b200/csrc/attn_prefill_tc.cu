@@ -86,6 +86,22 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, float* v) {
     for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
 }
 
+// The same 32 columns back into tensor memory.
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const float* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 ::"r"(taddr), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])), "r"(__float_as_uint(v[3])),
+                   "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])), "r"(__float_as_uint(v[7])),
+                   "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])), "r"(__float_as_uint(v[11])),
+                   "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])), "r"(__float_as_uint(v[15])),
+                   "r"(__float_as_uint(v[16])), "r"(__float_as_uint(v[17])), "r"(__float_as_uint(v[18])), "r"(__float_as_uint(v[19])),
+                   "r"(__float_as_uint(v[20])), "r"(__float_as_uint(v[21])), "r"(__float_as_uint(v[22])), "r"(__float_as_uint(v[23])),
+                   "r"(__float_as_uint(v[24])), "r"(__float_as_uint(v[25])), "r"(__float_as_uint(v[26])), "r"(__float_as_uint(v[27])),
+                   "r"(__float_as_uint(v[28])), "r"(__float_as_uint(v[29])), "r"(__float_as_uint(v[30])), "r"(__float_as_uint(v[31]))
+                 : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory descriptors (sm_100 version, 128-byte swizzle).
 // K-major tile [rows][64 elements]: rows 128 bytes apart, groups of eight rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t desc_k_major(const void* tile) {
@@ -198,10 +214,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         tma_load_2d(v_s + (i & 1) * STAGE + KV_ATOM, &map_v, 64, y, bar);
     };
 
-    float m_run = -INFINITY, l_run = 0.f;
-    float acc[PT_D];
-#pragma unroll
-    for (int d = 0; d < PT_D; ++d) acc[d] = 0.f;
+    // The output accumulates in tensor memory across pages.  The probabilities of a page are taken
+    // relative to a reference maximum m_ref that is raised only when the row's maximum exceeds it by more
+    // than 8 (in the log2 domain): then the row's sum and its accumulator are rescaled once.  Until then
+    // a probability may be as large as 2^8, which bfloat16 and the 32-bit sums hold without loss, and
+    // the final division by the sum removes the common factor.
+    float m_ref = -INFINITY, l_run = 0.f;
+    const int lo_max = window > 0 ? max(0, pos_max - window + 1) : 0;
 
     if (tid == 0) issue_page(0);
     uint32_t kv_phase[2] = {0, 0}, s_phase = 0, o_phase = 0;
@@ -228,22 +247,44 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         s_phase ^= 1;
         tc_fence_after();
 
-        // This thread's row of scores: mask, running maximum and sum, probabilities to shared memory.
+        // This thread's row of scores: mask (only where the page is not wholly visible), maximum, probabilities.
         const int key0 = (first_page + i) * SB_PAGE;
         float s[SB_PAGE];
         tc_ld32(tmem_row, s);
         tc_ld32(tmem_row + 32, s + 32);
+        const bool whole_page_visible = key0 + SB_PAGE - 1 <= pos_min && key0 >= lo_max && t_last == t0 + PT_ROWS - 1;
         float mx = -INFINITY;
+        if (whole_page_visible) {
 #pragma unroll
-        for (int c = 0; c < SB_PAGE; ++c) {
-            const int n = key0 + c;
-            s[c] = (n <= pos && n >= lo) ? s[c] * scale_log2 : -INFINITY;
-            mx = fmaxf(mx, s[c]);
+            for (int c = 0; c < SB_PAGE; ++c) mx = fmaxf(mx, s[c]);
+            mx *= scale_log2;   // scale_log2 > 0: the maximum commutes with it
+        } else {
+#pragma unroll
+            for (int c = 0; c < SB_PAGE; ++c) {
+                const int n = key0 + c;
+                if (!(n <= pos && n >= lo)) s[c] = -INFINITY;
+                mx = fmaxf(mx, s[c]);
+            }
+            mx *= scale_log2;
         }
-        const float m_new = fmaxf(m_run, mx);
-        const float m_safe = m_new == -INFINITY ? 0.f : m_new;
-        const float alpha = exp2f(m_run - m_safe);
-        m_run = m_new;
+        float alpha = 1.0f;
+        if (mx > m_ref + 8.0f || m_ref == -INFINITY) {
+            const float m_new = fmaxf(m_ref, mx);
+            alpha = m_new == -INFINITY ? 1.0f : exp2f(m_ref - m_new);   // 0 when the reference was -inf
+            m_ref = m_new;
+        }
+        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+        // the accumulator of earlier pages moves to the new reference (rare after the first pages)
+        if (i > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+            for (int d0 = 0; d0 < PT_D; d0 += 32) {
+                float o[32];
+                tc_ld32(tmem_row + SB_PAGE + d0, o);
+#pragma unroll
+                for (int d = 0; d < 32; ++d) o[d] *= alpha;
+                tc_st32(tmem_row + SB_PAGE + d0, o);
+            }
+        }
         float sum = 0.f;
 #pragma unroll
         for (int c = 0; c < SB_PAGE; c += 8) {
@@ -251,7 +292,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                const float p0 = exp2f(s[c + 2 * e] - m_safe), p1 = exp2f(s[c + 2 * e + 1] - m_safe);
+                const float p0 = exp2f(fmaf(s[c + 2 * e], scale_log2, -m_use)), p1 = exp2f(fmaf(s[c + 2 * e + 1], scale_log2, -m_use));
                 sum += p0 + p1;
                 h2[e] = __floats2bfloat162_rn(p0, p1);
             }
@@ -267,38 +308,38 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             const unsigned char* vt = v_s + stage * STAGE;
 #pragma unroll
             for (int ks = 0; ks < SB_PAGE / 16; ++ks)   // 16 keys per step: 32 bytes along P's rows, two groups of eight key rows of V
-                tc_mma(tmem + SB_PAGE, desc_k_major(p_s) + 2 * ks, desc_mn_major(vt + ks * 2048, KV_ATOM), idesc_o, ks > 0 ? 1u : 0u);
+                tc_mma(tmem + SB_PAGE, desc_k_major(p_s) + 2 * ks, desc_mn_major(vt + ks * 2048, KV_ATOM), idesc_o,
+                       (i > 0 || ks > 0) ? 1u : 0u);
             tc_commit(o_done);
         }
+        // The product must be done before the next page rescales the accumulator, overwrites P or reuses the stage.
         mbar_wait(o_done, o_phase, abort_flag, status);
         o_phase ^= 1;
         tc_fence_after();
-#pragma unroll
-        for (int d0 = 0; d0 < PT_D; d0 += 32) {
-            float o[32];
-            tc_ld32(tmem_row + SB_PAGE + d0, o);
-#pragma unroll
-            for (int d = 0; d < 32; ++d) acc[d0 + d] = fmaf(acc[d0 + d], alpha, o[d]);
-        }
-        tc_fence_before();
-        __syncthreads();   // everyone has read S and O_page: the next page may overwrite them
-        if (*abort_flag) break;
+        // (a time-out here is acted on after the next block-wide barrier, where all threads see it together)
     }
     pdl_launch_dependents();
     if (*abort_flag && tid == 0) {   // leaving early: give the copy in flight a bounded time to land
         const long long t_abort = clock64();
         while (clock64() - t_abort < (1ll << 22)) {}
     }
-    if (t < total && !*abort_flag) {
+    if (!*abort_flag) {
         const float inv = 1.0f / l_run;
-        __nv_bfloat16* o = out + ((long long)(row0 + t / G) * n_heads + kvh * G + t % G) * PT_D;
+        __nv_bfloat16* o_row = out + ((long long)(row0 + (t < total ? t / G : 0)) * n_heads + kvh * G + (t < total ? t % G : 0)) * PT_D;
 #pragma unroll
-        for (int d = 0; d < PT_D; d += 8) {
-            uint4 packed;
-            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+        for (int d0 = 0; d0 < PT_D; d0 += 32) {
+            float o[32];
+            tc_ld32(tmem_row + SB_PAGE + d0, o);
+            if (t < total) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(acc[d + 2 * e] * inv, acc[d + 2 * e + 1] * inv);
-            *reinterpret_cast<uint4*>(o + d) = packed;
+                for (int d = 0; d < 32; d += 8) {
+                    uint4 packed;
+                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
+                    *reinterpret_cast<uint4*>(o_row + d0 + d) = packed;
+                }
+            }
         }
     }
     tc_fence_before();
