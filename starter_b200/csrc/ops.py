@@ -303,6 +303,8 @@ class Ops:
         wdt = _code(q_norm.dtype) if q_norm is not None else dt
         if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
             raise KernelError("qk_norm_rope_store: qkv has the wrong width")
+        if head_dim > 512:
+            raise KernelError(f"qk_norm_rope_store takes head sizes up to 512, not {head_dim}")
         q = torch.empty((qkv.shape[0], n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
         cos = sin = None
         rotary_dim = 0
@@ -355,6 +357,10 @@ class Ops:
         everything else.  Other head sizes and float32 take the general kernel."""
         out = torch.empty_like(q)
         kv = self._kv(layer_cache)
+        if kv.head_dim > 256:
+            raise KernelError(f"attention takes head sizes up to 256, not {kv.head_dim}")
+        if n_heads % kv.n_kv_heads:
+            raise KernelError(f"{n_heads} query heads cannot share {kv.n_kv_heads} key/value heads evenly")
         if q.dtype == torch.bfloat16 and kv.head_dim in (64, 128):
             decode = ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and n_heads // kv.n_kv_heads <= 16
             pairs = ctx.n_seqs * kv.n_kv_heads

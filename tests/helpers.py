@@ -60,7 +60,17 @@ def run_tail_by_one(sess, seqs, tail=32):
     return outs
 
 
-def run_ragged_batches(sess, seqs, batch_size, prefix_fraction=0.5):
+def poison_cache(sess):
+    """Fill every key/value page with NaN (only when no sequence is live): a read of a page that a
+    finished sequence left behind then shows in the logits."""
+    assert sess.cache.slots.n_held == 0
+    for g in sess.cache.groups:
+        if hasattr(g, "k"):
+            g.k.fill_(float("nan"))
+            g.v.fill_(float("nan"))
+
+
+def run_ragged_batches(sess, seqs, batch_size, prefix_fraction=0.5, poison=False):
     """Batches of unequal requests, one after another: a ragged first step with a prefix of each
     request, then one token per live request per step; shorter requests end earlier and leave."""
     outs = [None] * len(seqs)
@@ -88,6 +98,8 @@ def run_ragged_batches(sess, seqs, batch_size, prefix_fraction=0.5):
             sess.cache.free(slots.pop(i))
         for i in ids:
             outs[i] = torch.cat(parts[i]).float().cpu()
+        if poison:
+            poison_cache(sess)
     sess.stepper.raise_on_status()
     sess.cache.check()
     return outs

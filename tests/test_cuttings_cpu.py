@@ -21,5 +21,6 @@ def test_every_cutting_matches_plain(tiny_folders, name, dtype):
     assert_close(run_whole(sess, seqs), ref, dtype, "alone and whole")
     assert_close(run_whole(sess, seqs[:3], together=True), ref[:3], dtype, "one ragged step")
     assert_close(run_tail_by_one(sess, seqs), ref, dtype, "tail one by one")
-    assert_close(run_ragged_batches(sess, seqs, batch_size=3), ref, dtype, "ragged batches")
+    assert_close(run_ragged_batches(sess, seqs, batch_size=3, poison=True), ref, dtype, "ragged batches, freed pages poisoned")
+    assert_close(run_whole(sess, seqs[:2]), ref[:2], dtype, "whole again, in poisoned slots")
     assert sess.cache.slots.n_held == 0

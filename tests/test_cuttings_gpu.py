@@ -19,5 +19,18 @@ def test_every_cutting_matches_plain(tiny_folders, name, dtype):
     assert_close(run_whole(sess, seqs), ref, dtype, "alone and whole")
     assert_close(run_whole(sess, seqs[:3], together=True), ref[:3], dtype, "one ragged step")
     assert_close(run_tail_by_one(sess, seqs), ref, dtype, "tail one by one")
-    assert_close(run_ragged_batches(sess, seqs, batch_size=3), ref, dtype, "ragged batches")
+    assert_close(run_ragged_batches(sess, seqs, batch_size=3, poison=True), ref, dtype, "ragged batches, freed pages poisoned")
+    assert_close(run_whole(sess, seqs[:2]), ref[:2], dtype, "whole again, in poisoned slots")
     assert sess.cache.slots.n_held == 0
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_first_tokens_of_a_sequence(tiny_folders, dtype):
+    """Sequences of one, two and three tokens, alone and in one step: position 0 has a single key."""
+    folder = tiny_folders["B"]
+    seqs = random_tokens(TINY["B"]["vocab_size"], (1, 2, 3, 1), seed=13)
+    ref = plain_logits(folder, seqs, dtype)
+    sess = make_session(folder, dtype, max_tokens=64 * 4, max_seqs=4)
+    assert_close(run_whole(sess, seqs), ref, dtype, "alone")
+    assert_close(run_whole(sess, seqs, together=True), ref, dtype, "together")
+    assert_close(run_tail_by_one(sess, seqs), ref, dtype, "token by token")

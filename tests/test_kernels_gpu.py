@@ -322,3 +322,37 @@ def test_rope_store_head_128_with_32_bit_norm_weights(ops, ref):
     close(outs[0], outs[1], dtype, "q", rel=8e-3)
     close(caches[0].groups[0].k, caches[1].groups[0].k, dtype, "stored keys", rel=8e-3)
     assert torch.equal(caches[0].groups[0].v, caches[1].groups[0].v)
+
+
+@pytest.mark.parametrize("dtype,head_dim", [(torch.float32, 32), (torch.bfloat16, 128), (torch.bfloat16, 64)])
+def test_attention_respects_the_window_edge(ops, dtype, head_dim):
+    """A huge key just outside the window must not count; the same key just inside must win.
+    Checked for a long piece (prefill kernels) and for a single new token (decode kernels)."""
+    heads, window, n = 4, 70, 200
+    for q_len in (n, 1):
+        for inside in (False, True):
+            cache = Cache([KVRequest(1, head_dim, window)], n_slots=1, max_tokens=64 * 5, dtype=dtype, device="cuda",
+                          max_step_tokens=256)
+            slot = cache.alloc()
+            cache.reserve(slot, n)
+            cache.flush()
+            qkv = rand((n, (heads + 2) * head_dim), dtype, 110, 0.05)
+            edge = n - 1 - window + (1 if inside else 0)         # the last query sees keys edge+1 .. n-1 (or edge .. n-1)
+            qkv[edge, heads * head_dim:(heads + 1) * head_dim] = 6.0
+            qkv[-1, :heads * head_dim] = 6.0
+            if q_len == n:
+                ctx = make_ctx(cache, ops, [slot], [n], dtype)
+                q = ops.qk_norm_rope_store(ctx, qkv, cache.layers[0], heads, 1, head_dim, None, None, 0.0, None)
+                a = ops.attention(ctx, q, cache.layers[0], heads, 1.0, window)
+            else:
+                ctx = make_ctx(cache, ops, [slot], [n - 1], dtype)
+                ops.qk_norm_rope_store(ctx, qkv[:-1].contiguous(), cache.layers[0], heads, 1, head_dim, None, None, 0.0, None)
+                ops.advance_lengths(ctx)
+                cache.advance_host(slot, n - 1)
+                ctx = make_ctx(cache, ops, [slot], [1], dtype)
+                q = ops.qk_norm_rope_store(ctx, qkv[-1:].contiguous(), cache.layers[0], heads, 1, head_dim, None, None, 0.0, None)
+                a = ops.attention(ctx, q, cache.layers[0], heads, 1.0, window)
+            value_at_edge = qkv[edge, (heads + 1) * head_dim:].float()
+            got = a[-1, :head_dim].float()
+            is_edge_value = float((got - value_at_edge).abs().max()) < 0.05 * float(value_at_edge.abs().max()) + 1e-3
+            assert is_edge_value == inside, f"q_len {q_len}, key {'inside' if inside else 'outside'} the window"
