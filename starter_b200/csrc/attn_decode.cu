@@ -163,7 +163,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
         __syncwarp();
     }
     cp_async_wait<0>();
-    pdl_launch_dependents();   // the keys are read; the next kernel may set itself up during the merge
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);

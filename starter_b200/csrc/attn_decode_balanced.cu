@@ -293,7 +293,6 @@ attn_decode_balanced_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
         }
         u += my_pages;
     }
-    pdl_launch_dependents();
 }
 
 template <int D> static int launch_balanced(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale,

@@ -193,7 +193,6 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
         __syncthreads();  // everyone is done with this stage before the copy after next lands in it
     }
     cp_async_wait<0>();
-    pdl_launch_dependents();
 
 #pragma unroll
     for (int h = 0; h < 2; ++h) {

@@ -318,7 +318,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         tc_fence_after();
         // (a time-out here is acted on after the next block-wide barrier, where all threads see it together)
     }
-    pdl_launch_dependents();
     if (*abort_flag && tid == 0) {   // leaving early: give the copy in flight a bounded time to land
         const long long t_abort = clock64();
         while (clock64() - t_abort < (1ll << 22)) {}

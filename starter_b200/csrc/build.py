@@ -110,7 +110,9 @@ def _compile_one(nvcc: str, src: Path, obj: Path, extra_flags) -> float:
 
 
 def build(verbose: bool = True, force: bool = False, extra_flags=()) -> Path:
-    """Compile what is out of date and link the library; returns its path."""
+    """Compile what is out of date and link the library; returns its path.  STARTER_B200_NVCC_FLAGS in the
+    environment adds flags (for experiments: a changed flag rebuilds everything)."""
+    extra_flags = tuple(extra_flags) + tuple(os.environ.get("STARTER_B200_NVCC_FLAGS", "").split())
     folder = build_dir()
     lib = folder / LIB_NAME
     hdr_digest = _digest(headers(), " ".join([*ARCH_FLAGS, *NVCC_FLAGS, *extra_flags]))

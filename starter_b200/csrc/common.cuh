@@ -98,7 +98,11 @@ __device__ __forceinline__ long long kv_offset(const SbKV& kv, int slot, int pos
 // it in the stream is still running; it must call pdl_wait() before it reads anything that kernel
 // wrote (or writes anything that kernel reads).  What comes before the wait (fetching weights, setting
 // up barriers) overlaps the predecessor's tail.  pdl_launch_dependents() lets the next kernel in the
-// stream start its own preamble.  Without the attribute both are no-ops.
+// stream start its own preamble before this one has ended; a kernel that never calls it releases its
+// successor when it ends.  Without the attribute both are no-ops.
+// Measured on a decode step of 36 layers at batch 8 (B200): attribute and waits alone 3.32 ms against
+// 3.45 ms without; the early release in the matrix products as well 3.30 ms (and 369 against 358 tokens
+// a second at batch 1); an early release in the attention kernels as well 3.55 ms, so they have none.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -126,6 +126,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
             pdl_wait();
             turn(lo, hi, kt);
         }
+        pdl_wait();   // a warp without a turn of its own waits too, before anything is written
     }
 
     pdl_launch_dependents();   // the weights are read; the next kernel may start fetching its own

@@ -1,6 +1,7 @@
 """The engine on the GPU against the plain implementation, in every way of cutting the work."""
 
 import pytest
+import torch
 
 from conftest import TINY, random_tokens
 from helpers import assert_close, make_session, plain_logits, run_ragged_batches, run_tail_by_one, run_whole
@@ -34,3 +35,18 @@ def test_first_tokens_of_a_sequence(tiny_folders, dtype):
     assert_close(run_whole(sess, seqs), ref, dtype, "alone")
     assert_close(run_whole(sess, seqs, together=True), ref, dtype, "together")
     assert_close(run_tail_by_one(sess, seqs), ref, dtype, "token by token")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_dependent_launch_changes_no_bit(tiny_folders, dtype):
+    """Kernels that may start before their predecessor has ended (the default) give the very same logits as
+    kernels that run strictly one after another: every one of them waits before it touches earlier results."""
+    folder = tiny_folders["A"]
+    seqs = random_tokens(TINY["A"]["vocab_size"], (150, 9, 64), seed=17)
+    got = {}
+    for on in (False, True):
+        sess = make_session(folder, dtype, max_tokens=64 * 8, max_seqs=4, dependent_launch=on)
+        got[on] = run_whole(sess, seqs, together=True) + run_tail_by_one(sess, seqs)
+    for a, b in zip(got[False], got[True]):
+        assert torch.equal(a, b)
+    assert_close(got[True][:3], plain_logits(folder, seqs, dtype), dtype, "dependent launch")
