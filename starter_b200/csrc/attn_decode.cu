@@ -34,8 +34,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
     __shared__ int s_is_last;
     unsigned char* q_s = smem;                             // [16][D] bfloat16
     unsigned char* pipe = smem + 16 * D * 2;               // [warp][stage][K slice | V slice]
-    pdl_wait();
 
+    // Until pdl_wait() only what the kernel before this one does not write is touched: the batch's description,
+    // the lengths, the page table, and pages before the one that holds the new token.  That kernel (the
+    // rotary kernel that stores the new key and value) releases this one as soon as it runs, so the
+    // look-ups and the first copies below overlap it.
     const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = n_heads / kv.n_kv_heads;
@@ -49,19 +52,6 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
     const int p_begin = first_page + split * per_split;
     const int p_end = min(p_begin + per_split, last_page + 1);
     const int my_pages = max(p_end - p_begin, 0);
-
-    // Query heads of this kv head as rows of a 16-row tile, zero beyond G.
-    for (int i = tid; i < 16 * CH; i += AD_WARPS * 32) {
-        const int r = i / CH, c = i % CH;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < G) v = *reinterpret_cast<const uint4*>(q + ((long long)row * n_heads + kvh * G + r) * D + c * 8);
-        *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
-    }
-    __syncthreads();
-    unsigned int qf[D / 16][4];
-#pragma unroll
-    for (int ks = 0; ks < D / 16; ++ks)
-        ldmatrix_x4(qf[ks], q_s + tile_off<D>((lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
 
     unsigned char* my_pipe = pipe + warp * (AD_STAGES * 2 * SLICE);
     const __nv_bfloat16* kbase = (const __nv_bfloat16*)kv.k;
@@ -98,8 +88,24 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
 #pragma unroll
     for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
+    int ahead = 0;
+    while (ahead < AD_STAGES - 1 && p_begin + ahead < last_page) issue(ahead++);
+    pdl_wait();
+    for (; ahead < AD_STAGES - 1; ++ahead) issue(ahead);   // the page of the new token, after the wait
+
+    // Query heads of this kv head as rows of a 16-row tile, zero beyond G.
+    for (int i = tid; i < 16 * CH; i += AD_WARPS * 32) {
+        const int r = i / CH, c = i % CH;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < G) v = *reinterpret_cast<const uint4*>(q + ((long long)row * n_heads + kvh * G + r) * D + c * 8);
+        *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
+    }
+    __syncthreads();
+    unsigned int qf[D / 16][4];
 #pragma unroll
-    for (int i = 0; i < AD_STAGES - 1; ++i) issue(i);
+    for (int ks = 0; ks < D / 16; ++ks)
+        ldmatrix_x4(qf[ks], q_s + tile_off<D>((lane & 7) + ((lane >> 3) & 1) * 8, ks * 2 + (lane >> 4)));
+
     for (int i = 0; i < my_pages; ++i) {
         issue(i + AD_STAGES - 1);
         cp_async_wait<AD_STAGES - 1>();

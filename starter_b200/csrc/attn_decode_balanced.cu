@@ -20,7 +20,7 @@
 #define ADB_MAX_SEQS 1024
 
 template <int D>
-__global__ void __launch_bounds__(AD_WARPS * 32, 2)
+__global__ void __launch_bounds__(AD_WARPS * 32, 1)
 attn_decode_balanced_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, SbBatch batch, SbKV kv,
                             int n_heads, float scale_log2, int window, float* __restrict__ partial,
                             int* __restrict__ counters) {
@@ -32,8 +32,9 @@ attn_decode_balanced_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
     __shared__ int cum[ADB_MAX_SEQS + 1];                  // units before each sequence
     unsigned char* q_s = smem;                             // [16][D] bfloat16
     unsigned char* pipe = smem + 16 * D * 2;               // [warp][stage][K slice | V slice]
-    pdl_wait();
 
+    // The shares are worked out from the lengths, which the kernel before this one does not write, so
+    // this part may overlap it; everything after pdl_wait() may read what it wrote.
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = n_heads / kv.n_kv_heads, HKV = kv.n_kv_heads;
     const int B = batch.n_seqs;
@@ -48,6 +49,7 @@ attn_decode_balanced_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
         for (int i = 0; i < B; ++i) cum[i + 1] += cum[i];
     }
     __syncthreads();
+    pdl_wait();
     const int U = cum[B], P = gridDim.x;
     const int quota = (U + P - 1) / P;
     int u = blockIdx.x * quota;
@@ -299,7 +301,11 @@ template <int D> static int launch_balanced(const void* q, void* out, SbBatch ba
                                             int window, int grid, float* partial, int* counters, cudaStream_t stream) {
     const int pipe_bytes = AD_WARPS * AD_STAGES * 2 * AD_KEYS_PER_WARP * D * 2;
     const int merge_bytes = (AD_WARPS * 16 * D + 2 * AD_WARPS * 16) * 4;
-    const int smem = 16 * D * 2 + (pipe_bytes > merge_bytes ? pipe_bytes : merge_bytes);
+    // More than half an SM's shared memory is asked for, so that no SM ever holds two of these blocks: the
+    // shares are equal only if every block has an SM to itself, also when the grid starts while the kernel
+    // before it still holds some SMs.
+    const int need = 16 * D * 2 + (pipe_bytes > merge_bytes ? pipe_bytes : merge_bytes);
+    const int smem = need > 116 * 1024 ? need : 116 * 1024;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_balanced_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);

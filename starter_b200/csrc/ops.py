@@ -364,9 +364,10 @@ class Ops:
         if q.dtype == torch.bfloat16 and kv.head_dim in (64, 128):
             decode = ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and n_heads // kv.n_kv_heads <= 16
             pairs = ctx.n_seqs * kv.n_kv_heads
-            if decode and self.decode_balanced and pairs > self.decode_resident(kv.head_dim) and ctx.n_seqs <= 1024:
+            force = os.environ.get("STARTER_B200_ATTN") == "force_balanced"
+            if decode and self.decode_balanced and (pairs > self.decode_resident(kv.head_dim) or force) and ctx.n_seqs <= 1024:
                 # More pairs than blocks fit at once: one block per SM, each with an equal share of all pages.
-                grid = min(int(os.environ.get("STARTER_B200_ATTN_GRID", 1)) * self.sm_count(), 512)
+                grid = min(self.sm_count(), 512)
                 key = ("attn_decode_balanced", q.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, grid)
                 buf = self._scratch.get(key)
                 if buf is None:

@@ -20,6 +20,7 @@ __global__ void qk_rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
                                      const T* __restrict__ sin_t, int rotary_dim, int* status) {
     __shared__ float y[QK_MAX_D];
     pdl_wait();
+    pdl_launch_dependents();   // the attention that follows looks up its pages and fetches old keys meanwhile
     const int row = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
     const int D = kv.head_dim;
     const int width = (n_heads + 2 * n_kv_heads) * D;
@@ -86,6 +87,7 @@ qk_rope_store_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
                           float eps, const __nv_bfloat16* __restrict__ cos_t, const __nv_bfloat16* __restrict__ sin_t,
                           int* status) {
     pdl_wait();
+    pdl_launch_dependents();   // the attention that follows looks up its pages and fetches old keys meanwhile
     const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int width = (n_heads + 2 * n_kv_heads) * 128;
     int slot, pos;

@@ -12,6 +12,7 @@ template <class T>
 __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict__ table, T* __restrict__ out,
                              int hidden, int vocab, int* status) {
     pdl_wait();
+    pdl_launch_dependents();   // a small kernel: its successor may fetch its weights meanwhile
     const int row = blockIdx.x;
     int tok = tokens[row];
     if (tok < 0 || tok >= vocab) {
@@ -26,6 +27,7 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const T* __restrict
 template <class T>
 __global__ void gather_rows_kernel(const T* __restrict__ x, const int* __restrict__ rows, T* __restrict__ out, int width) {
     pdl_wait();
+    pdl_launch_dependents();
     const T* src = x + (long long)rows[blockIdx.x] * width;
     T* dst = out + (long long)blockIdx.x * width;
     for (int c = threadIdx.x; c < width; c += blockDim.x) dst[c] = src[c];
@@ -37,6 +39,7 @@ __global__ void rmsnorm_kernel(T* __restrict__ x, const T* __restrict__ delta, c
                                T* __restrict__ out, int width, float eps) {
     __shared__ float red[33];
     pdl_wait();
+    pdl_launch_dependents();   // the product that follows fetches its first weights while the rows are normed
     T* xr = x + (long long)blockIdx.x * width;
     const T* dr = ADD ? delta + (long long)blockIdx.x * width : nullptr;
     T* yr = out + (long long)blockIdx.x * width;
@@ -64,6 +67,7 @@ __global__ void rmsnorm_vec_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfl
                                    const W* __restrict__ weight, __nv_bfloat16* __restrict__ out, int width, float eps) {
     __shared__ float red[33];
     pdl_wait();
+    pdl_launch_dependents();
     const long long base = (long long)blockIdx.x * width;
     const int c = threadIdx.x * 8;
     const bool active = c < width;
