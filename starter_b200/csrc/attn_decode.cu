@@ -1,5 +1,5 @@
 // Decode attention over the paged cache: one new token per sequence, grouped query heads,
-// keys split across thread blocks, partial results merged by the last block to finish.
+// keys split across thread blocks, partial results merged at the end.
 //
 // Reference: engine/kernels/attention.py:24-114 (split-K flash decoding: all G = heads /
 // kv_heads query heads of a key/value head share one program so that keys and values are
@@ -13,32 +13,81 @@
 // (mma.sync m16n8k16, bfloat16 in, 32-bit accumulate) see the G query heads as the rows of a
 // 16-row tile.  The split count depends on shapes only; the pages are divided among the
 // splits on the device from the sequence's own length, so a graph replay stays valid as the
-// sequence grows.  With more than one split each block leaves its partial result in scratch
-// memory and the last one to arrive (an atomic counter per sequence and kv head) merges them.
+// sequence grows.
+//
+// Merging the splits.  With 2 to 8 splits the blocks of one (sequence, kv head) form a thread-block
+// cluster: each leaves its result in its own shared memory, the cluster meets, and every block
+// finishes a share of the output from the others' shared memory (no trip through global memory, no
+// atomic).  With more splits each block leaves its partial result in scratch memory and the last one
+// to arrive (an atomic counter per sequence and kv head) merges them.
+//
+// Fused preparation of q and k (FUSED).  The kernel can take the row of the fused q/k/v projection
+// instead of finished queries: it then applies the per-head RMSNorm and the rotary encoding to its own
+// G query heads (engine/kernels/rope.py:95-144), and the block whose pages hold the new token's
+// position does the same for the key head, stores key and value in the cache and reads them back with
+// its other keys.  That saves the separate kernel between the projection and the attention.
+#include <cooperative_groups.h>
+
 #include "common.cuh"
 #include "mma_utils.cuh"
+
+namespace cg = cooperative_groups;
 
 #define AD_WARPS 4
 #define AD_STAGES 2
 #define AD_KEYS_PER_WARP (SB_PAGE / AD_WARPS)  // 16
+#define AD_MAX_CLUSTER 8
 
-template <int D>
+// What the fused preparation needs besides the cache.  qkv [rows, (n_heads + 2 * n_kv_heads) * D], or
+// [rows, n_heads * D] when store_kv is 0 (a layer that reads another layer's cache); norm weights
+// bfloat16 or float (norm_f32), null = no per-head norm; cos/sin [positions, D / 2] bfloat16, null = no
+// rotary encoding (otherwise over the whole head).
+struct SbFusedQK {
+    const __nv_bfloat16* qkv;
+    const void* q_norm;
+    const void* k_norm;
+    const __nv_bfloat16* cos_t;
+    const __nv_bfloat16* sin_t;
+    int* status;
+    float eps;
+    int norm_f32;
+    int store_kv;
+    int reserved;
+};
+
+__device__ __forceinline__ void unpack4(const uint2 raw, float (&v)[4]) {
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+
+__device__ __forceinline__ void load_norm4(const void* w, int norm_f32, int d0, float (&v)[4]) {
+    if (norm_f32) {
+        const float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + d0);
+        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
+    } else {
+        unpack4(*reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(w) + d0), v);
+    }
+}
+
+template <int D, bool FUSED>
 __global__ void __launch_bounds__(AD_WARPS * 32)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, SbBatch batch, SbKV kv,
-                   int n_heads, float scale_log2, int window, int n_splits, float* __restrict__ partial,
-                   int* __restrict__ counters) {
+                   int n_heads, float scale_log2, int window, int n_splits, int cluster_merge, float* __restrict__ partial,
+                   int* __restrict__ counters, SbFusedQK fused) {
     constexpr int CH = D / 8;                              // 16-byte chunks per row
     constexpr int SLICE = AD_KEYS_PER_WARP * D * 2;        // bytes of one warp's keys (or values) of a page
     constexpr int NT = D / 8;                              // output n-tiles of 8 columns
+    constexpr int LANES = D / 4;                           // lanes that hold a head, four values each
     extern __shared__ __align__(128) unsigned char smem[];
     __shared__ int s_is_last;
     unsigned char* q_s = smem;                             // [16][D] bfloat16
     unsigned char* pipe = smem + 16 * D * 2;               // [warp][stage][K slice | V slice]
 
     // Until pdl_wait() only what the kernel before this one does not write is touched: the batch's description,
-    // the lengths, the page table, and pages before the one that holds the new token.  That kernel (the
-    // rotary kernel that stores the new key and value) releases this one as soon as it runs, so the
-    // look-ups and the first copies below overlap it.
+    // the lengths, the page table, the norm weights and rotary tables, and pages before the one that holds
+    // the new token.  If that kernel releases this one early, the look-ups and first copies below overlap it.
+    sb_stamp(4, 0);
     const int seq = blockIdx.x, kvh = blockIdx.y, split = blockIdx.z;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = n_heads / kv.n_kv_heads;
@@ -88,19 +137,96 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
 #pragma unroll
     for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
 
+    // Constants of the fused preparation: this lane's four rotary factors and norm weights, and where the
+    // new key and value go (only the block whose pages hold the new position stores them).
+    const int d0 = lane * 4;
+    const bool holds = lane < LANES;
+    float rc[4] = {1.f, 1.f, 1.f, 1.f}, rs[4] = {0.f, 0.f, 0.f, 0.f}, wq[4] = {1.f, 1.f, 1.f, 1.f};
+    bool owns_new = false;
+    long long new_off = -1;
+    if (FUSED) {
+        if (holds) {
+            if (fused.cos_t != nullptr) {
+                const int j0 = d0 % (D / 2);
+                unpack4(*reinterpret_cast<const uint2*>(fused.cos_t + (long long)pos * (D / 2) + j0), rc);
+                unpack4(*reinterpret_cast<const uint2*>(fused.sin_t + (long long)pos * (D / 2) + j0), rs);
+            }
+            if (fused.q_norm != nullptr) load_norm4(fused.q_norm, fused.norm_f32, d0, wq);
+        }
+        owns_new = fused.store_kv && p_begin <= last_page && last_page < p_end;
+        if (owns_new) new_off = kv_offset(kv, slot, pos, kvh);
+    }
+
     int ahead = 0;
     while (ahead < AD_STAGES - 1 && p_begin + ahead < last_page) issue(ahead++);
+    sb_stamp(4, 1);
     pdl_wait();
-    for (; ahead < AD_STAGES - 1; ++ahead) issue(ahead);   // the page of the new token, after the wait
+    sb_stamp(4, 2);
 
-    // Query heads of this kv head as rows of a 16-row tile, zero beyond G.
-    for (int i = tid; i < 16 * CH; i += AD_WARPS * 32) {
-        const int r = i / CH, c = i % CH;
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < G) v = *reinterpret_cast<const uint4*>(q + ((long long)row * n_heads + kvh * G + r) * D + c * 8);
-        *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
+    if (FUSED) {
+        // Rows of the query tile beyond the group are zero.
+        for (int i = tid; i < 16 * CH; i += AD_WARPS * 32) {
+            const int r = i / CH, c = i % CH;
+            if (r >= G) *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = make_uint4(0u, 0u, 0u, 0u);
+        }
+        const int width = (n_heads + (fused.store_kv ? 2 * kv.n_kv_heads : 0)) * D;
+        const __nv_bfloat16* qkv_row = fused.qkv + (long long)row * width;
+        const int n_jobs = G + (owns_new ? 1 : 0);          // job G: the key head (and the value's copy)
+        for (int job = warp; job < n_jobs; job += AD_WARPS) {
+            const bool is_q = job < G;
+            const __nv_bfloat16* src = qkv_row + (long long)(is_q ? kvh * G + job : n_heads + kvh) * D;
+            float y[4] = {0.f, 0.f, 0.f, 0.f};
+            if (holds) unpack4(*reinterpret_cast<const uint2*>(src + d0), y);
+            const void* wn = is_q ? fused.q_norm : fused.k_norm;
+            if (wn != nullptr) {
+                float w4[4] = {wq[0], wq[1], wq[2], wq[3]};
+                if (!is_q && holds) load_norm4(wn, fused.norm_f32, d0, w4);
+                float ss = y[0] * y[0];
+                ss = fmaf(y[1], y[1], ss); ss = fmaf(y[2], y[2], ss); ss = fmaf(y[3], y[3], ss);
+                ss = warp_sum(ss);
+                const float rstd = 1.0f / sqrtf(ss / (float)D + fused.eps);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float n = rnd<__nv_bfloat16>(__fmul_rn(y[e], rstd));
+                    y[e] = rnd<__nv_bfloat16>(__fmul_rn(w4[e], n));
+                }
+            }
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                o[e] = y[e];
+                if (fused.cos_t != nullptr) {   // rotate-half: the partner of d is d +- D/2, held by lane ^ (LANES / 2)
+                    const float partner = __shfl_xor_sync(0xffffffffu, y[e], LANES / 2);
+                    const float a = rnd<__nv_bfloat16>(__fmul_rn(y[e], rc[e]));
+                    const float b = rnd<__nv_bfloat16>(__fmul_rn(lane < LANES / 2 ? -partner : partner, rs[e]));
+                    o[e] = __fadd_rn(a, b);
+                }
+            }
+            uint2 res;
+            __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
+            r2[0] = __floats2bfloat162_rn(o[0], o[1]);
+            r2[1] = __floats2bfloat162_rn(o[2], o[3]);
+            if (is_q) {
+                if (holds) *reinterpret_cast<uint2*>(q_s + tile_off<D>(job, lane >> 1) + (lane & 1) * 8) = res;
+            } else if (new_off < 0) {
+                if (lane == 0) atomicOr(fused.status, SB_STATUS_NO_PAGE);
+            } else if (holds) {
+                *reinterpret_cast<uint2*>((__nv_bfloat16*)kv.k + new_off + d0) = res;
+                *reinterpret_cast<uint2*>((__nv_bfloat16*)kv.v + new_off + d0) =
+                    *reinterpret_cast<const uint2*>(src + (long long)kv.n_kv_heads * D + d0);
+            }
+        }
+    } else {
+        // Query heads of this kv head as rows of a 16-row tile, zero beyond G.
+        for (int i = tid; i < 16 * CH; i += AD_WARPS * 32) {
+            const int r = i / CH, c = i % CH;
+            uint4 v = make_uint4(0u, 0u, 0u, 0u);
+            if (r < G) v = *reinterpret_cast<const uint4*>(q + ((long long)row * n_heads + kvh * G + r) * D + c * 8);
+            *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
+        }
     }
-    __syncthreads();
+    __syncthreads();   // the queries are in place; the new key and value are in the cache before their page is copied
+    for (; ahead < AD_STAGES - 1; ++ahead) issue(ahead);   // the page of the new token, after the wait
     unsigned int qf[D / 16][4];
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks)
@@ -169,6 +295,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
         __syncwarp();
     }
     cp_async_wait<0>();
+    sb_stamp(4, 3);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l[h] += __shfl_xor_sync(0xffffffffu, l[h], 1);
@@ -176,10 +303,14 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
     }
     __syncthreads();  // every warp is done with the pipeline's memory; it now holds the warps' states
 
-    // Warp states to shared memory: acc [warp][16][D] floats, then m and l [warp][16].
+    // Warp states to shared memory: acc [warp][16][D] floats, then m and l [warp][16]; behind them the
+    // block's own result for the cluster: o [G][D], m [16], l [16].
     float* w_acc = reinterpret_cast<float*>(pipe);
     float* w_m = w_acc + AD_WARPS * 16 * D;
     float* w_l = w_m + AD_WARPS * 16;
+    float* blk_o = w_l + AD_WARPS * 16;
+    float* blk_m = blk_o + 16 * D;
+    float* blk_l = blk_m + 16;
     {
         const int r0 = lane >> 2, c0 = (lane & 3) * 2;
 #pragma unroll
@@ -212,6 +343,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
         const int head = kvh * G + r;
         if (n_splits == 1) {
             out[((long long)row * n_heads + head) * D + d] = __float2bfloat16_rn(o / L);
+        } else if (cluster_merge) {
+            blk_o[i] = o;
+            if (d == 0) { blk_m[r] = M; blk_l[r] = L; }
         } else {
             float* p = partial + (((long long)seq * n_heads + head) * n_splits + split) * part_stride;
             p[d] = o;
@@ -219,6 +353,39 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
         }
     }
     if (n_splits == 1) return;
+
+    if (cluster_merge) {
+        // The blocks of this (sequence, kv head) are one cluster, this block's rank in it is its split.  Each
+        // finishes an equal share of the G * D outputs from all the blocks' shared memory.
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        sb_stamp(4, 4);
+        const int share = (G * D + n_splits - 1) / n_splits;
+        const int i_end = min(G * D, (split + 1) * share);
+        for (int i = split * share + tid; i < i_end; i += AD_WARPS * 32) {
+            const int r = i / D, d = i % D;
+            float ms[AD_MAX_CLUSTER];
+            float M = -INFINITY;
+#pragma unroll
+            for (int c = 0; c < AD_MAX_CLUSTER; ++c)
+                if (c < n_splits) {
+                    ms[c] = *cluster.map_shared_rank(blk_m + r, c);
+                    M = fmaxf(M, ms[c]);
+                }
+            float o = 0.f, L = 0.f;
+#pragma unroll
+            for (int c = 0; c < AD_MAX_CLUSTER; ++c)
+                if (c < n_splits) {
+                    const float wgt = ms[c] == -INFINITY ? 0.f : exp2f(ms[c] - M);
+                    o += *cluster.map_shared_rank(blk_o + i, c) * wgt;
+                    L += *cluster.map_shared_rank(blk_l + r, c) * wgt;
+                }
+            out[((long long)row * n_heads + kvh * G + r) * D + d] = __float2bfloat16_rn(o / L);
+        }
+        cluster.sync();   // nobody leaves while its shared memory is still being read
+        sb_stamp(4, 5);
+        return;
+    }
 
     // The last block of this (sequence, kv head) to get here merges the splits.
     __threadfence();
@@ -228,6 +395,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
         s_is_last = prev == n_splits - 1;
     }
     __syncthreads();
+    sb_stamp(4, 4);
     if (!s_is_last) return;
     __threadfence();
     // Weights of the splits first (each thread fetches other entries, so the loads overlap), then
@@ -276,31 +444,60 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
         out[((long long)row * n_heads + head) * D + d] = __float2bfloat16_rn(o / L);
     }
     if (tid == 0) counters[seq * kv.n_kv_heads + kvh] = 0;  // ready for the next launch
+    sb_stamp(4, 5);
 }
 
-template <int D> static int launch_decode(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale,
-                                          int window, int n_splits, float* partial, int* counters, cudaStream_t stream) {
+template <int D, bool FUSED>
+static int launch_decode(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale, int window, int n_splits,
+                         float* partial, int* counters, SbFusedQK fused, cudaStream_t stream) {
     const int pipe_bytes = AD_WARPS * AD_STAGES * 2 * AD_KEYS_PER_WARP * D * 2;
-    const int merge_bytes = (AD_WARPS * 16 * D + 2 * AD_WARPS * 16) * 4;
+    const int merge_bytes = (AD_WARPS * 16 * D + 2 * AD_WARPS * 16 + 16 * D + 32) * 4;
     const int smem = 16 * D * 2 + (pipe_bytes > merge_bytes ? pipe_bytes : merge_bytes);
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    dim3 grid(batch.n_seqs, kv.n_kv_heads, n_splits);
-    sb_launch(attn_decode_kernel<D>, grid, AD_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv,
-                                                                 n_heads, scale * 1.4426950408889634f, window, n_splits,
-                                                                 partial, counters);
-    return (int)cudaGetLastError();
+    const int cluster_merge = n_splits >= 2 && n_splits <= AD_MAX_CLUSTER;
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(batch.n_seqs, kv.n_kv_heads, n_splits);
+    config.blockDim = dim3(AD_WARPS * 32);
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n_attr = 0;
+    if (sb_pdl_flag) {
+        attr[n_attr].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n_attr].val.programmaticStreamSerializationAllowed = 1;
+        ++n_attr;
+    }
+    if (cluster_merge) {
+        attr[n_attr].id = cudaLaunchAttributeClusterDimension;
+        attr[n_attr].val.clusterDim.x = 1;
+        attr[n_attr].val.clusterDim.y = 1;
+        attr[n_attr].val.clusterDim.z = n_splits;
+        ++n_attr;
+    }
+    config.attrs = attr;
+    config.numAttrs = n_attr;
+    cudaError_t e = cudaLaunchKernelEx(&config, attn_decode_kernel<D, FUSED>, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch,
+                                       kv, n_heads, scale * 1.4426950408889634f, window, n_splits, cluster_merge, partial,
+                                       counters, fused);
+    return e != cudaSuccess ? (int)e : (int)cudaGetLastError();
+}
+
+static bool decode_shape_ok(const SbBatch& batch, const SbKV& kv, int n_heads, int n_splits) {
+    return batch.n_rows == batch.n_seqs && n_heads % kv.n_kv_heads == 0 && n_heads / kv.n_kv_heads <= 16 && n_splits >= 1 &&
+           n_splits <= 65535 && kv.n_kv_heads <= 65535 && (kv.head_dim == 64 || kv.head_dim == 128);
 }
 
 extern "C" {
 
-// Floats of scratch the kernel needs for a batch: partial results [seq][head][split][D + 2].
+// Floats of scratch the kernel needs for a batch: partial results [seq][head][split][D + 2]
+// (none with up to 8 splits, which merge through shared memory).
 long long sb_attn_decode_scratch_floats(int n_seqs, int n_heads, int head_dim, int n_splits) {
-    return n_splits > 1 ? (long long)n_seqs * n_heads * n_splits * (head_dim + 2) : 0;
+    return n_splits > AD_MAX_CLUSTER ? (long long)n_seqs * n_heads * n_splits * (head_dim + 2) : 0;
 }
 
 // One new token per sequence (rows == sequences).  q, out [rows, n_heads * head_dim] bfloat16.
@@ -310,12 +507,22 @@ long long sb_attn_decode_scratch_floats(int n_seqs, int n_heads, int head_dim, i
 int sb_attn_decode(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale, int window, int n_splits,
                    float* partial, int* counters, cudaStream_t stream) {
     if (batch.n_seqs <= 0) return 0;
-    if (batch.n_rows != batch.n_seqs || n_heads % kv.n_kv_heads || n_heads / kv.n_kv_heads > 16 || n_splits < 1 ||
-        n_splits > 65535 || kv.n_kv_heads > 65535)
+    if (!decode_shape_ok(batch, kv, n_heads, n_splits)) return (int)cudaErrorInvalidValue;
+    SbFusedQK none = {};
+    if (kv.head_dim == 128) return launch_decode<128, false>(q, out, batch, kv, n_heads, scale, window, n_splits, partial, counters, none, stream);
+    return launch_decode<64, false>(q, out, batch, kv, n_heads, scale, window, n_splits, partial, counters, none, stream);
+}
+
+// The same with the preparation of q and k inside (see the top of this file): qkv is the row of the fused
+// projection; the new key and value are stored in the cache by this call.
+int sb_attn_decode_fused(SbFusedQK fused, void* out, SbBatch batch, SbKV kv, int n_heads, float scale, int window, int n_splits,
+                         float* partial, int* counters, cudaStream_t stream) {
+    if (batch.n_seqs <= 0) return 0;
+    if (!decode_shape_ok(batch, kv, n_heads, n_splits) || fused.qkv == nullptr || fused.status == nullptr ||
+        ((fused.cos_t == nullptr) != (fused.sin_t == nullptr)))
         return (int)cudaErrorInvalidValue;
-    if (kv.head_dim == 128) return launch_decode<128>(q, out, batch, kv, n_heads, scale, window, n_splits, partial, counters, stream);
-    if (kv.head_dim == 64) return launch_decode<64>(q, out, batch, kv, n_heads, scale, window, n_splits, partial, counters, stream);
-    return (int)cudaErrorInvalidValue;
+    if (kv.head_dim == 128) return launch_decode<128, true>(nullptr, out, batch, kv, n_heads, scale, window, n_splits, partial, counters, fused, stream);
+    return launch_decode<64, true>(nullptr, out, batch, kv, n_heads, scale, window, n_splits, partial, counters, fused, stream);
 }
 
 }  // extern "C"
@@ -381,3 +588,5 @@ int sb_attn_decode_noalloc(const void* q, void* out, SbBatch batch, SbKV kv, int
 }
 
 }  // extern "C"
+
+SB_TIMELINE_SETTER(attn_decode)

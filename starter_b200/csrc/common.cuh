@@ -106,6 +106,28 @@ __device__ __forceinline__ long long kv_offset(const SbKV& kv, int slot, int pos
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Tuning aid, compiled in with -DSB_TIMELINE only: thread 0 of a block appends (time, kernel, milestone, block)
+// to a log on the device, from which a script draws the step's timeline.  Each source file has its own
+// pointer to the log, set through the function that SB_TIMELINE_SETTER defines for it.
+#ifdef SB_TIMELINE
+static __device__ unsigned long long* sb_tl_log = nullptr;   // [0] entries used, [1] capacity, then pairs (time, tag)
+__device__ __forceinline__ void sb_stamp(int kernel, int milestone) {
+    if (threadIdx.x != 0 || sb_tl_log == nullptr) return;
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    const unsigned long long i = atomicAdd(sb_tl_log, 1ull);
+    if (i >= sb_tl_log[1]) return;
+    const unsigned long long block = blockIdx.x + (unsigned long long)gridDim.x * (blockIdx.y + (unsigned long long)gridDim.y * blockIdx.z);
+    sb_tl_log[2 + 2 * i] = t;
+    sb_tl_log[3 + 2 * i] = ((unsigned long long)kernel << 48) | ((unsigned long long)milestone << 40) | block;
+}
+#define SB_TIMELINE_SETTER(name) \
+    extern "C" int sb_timeline_##name(void* log) { return (int)cudaMemcpyToSymbol(sb_tl_log, &log, sizeof(log)); }
+#else
+#define sb_stamp(kernel, milestone) ((void)0)
+#define SB_TIMELINE_SETTER(name)
+#endif
+
 extern int sb_pdl_flag;  // set through sb_set_pdl(); defined in rows.cu
 
 template <typename... Exp, typename... Act>

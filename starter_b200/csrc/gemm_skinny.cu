@@ -104,6 +104,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     };
     constexpr int STRIDE = WPG * GS_KWARP;
     int kt = k_begin + wk * GS_KWARP;
+    sb_stamp(2, 0);
     if (DEEP) {
         uint4 lo_a[4], hi_a[4], lo_b[4], hi_b[4];
         if (kt < k_end) load_w(lo_a, hi_a, kt);
@@ -129,6 +130,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         pdl_wait();   // a warp without a turn of its own waits too, before anything is written
     }
 
+    sb_stamp(2, 1);
     pdl_launch_dependents();   // the weights are read; the next kernel may start fetching its own
     // Warps meet: red[warp][weight row][activation row].
 #pragma unroll
@@ -186,6 +188,7 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         else
             reinterpret_cast<__nv_bfloat16*>(C)[o] = __float2bfloat16_rn(v);
     }
+    sb_stamp(2, 2);
 }
 
 extern "C" {
@@ -231,3 +234,5 @@ int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int 
 }
 
 }  // extern "C"
+
+SB_TIMELINE_SETTER(skinny)

@@ -35,6 +35,11 @@ class SbKV(Structure):
                 ("ring_pages", c_int), ("n_kv_heads", c_int), ("head_dim", c_int)]
 
 
+class SbFusedQK(Structure):
+    _fields_ = [("qkv", c_void_p), ("q_norm", c_void_p), ("k_norm", c_void_p), ("cos_t", c_void_p), ("sin_t", c_void_p),
+                ("status", c_void_p), ("eps", c_float), ("norm_f32", c_int), ("store_kv", c_int), ("reserved", c_int)]
+
+
 def _code(dtype: torch.dtype) -> int:
     if dtype == torch.float32:
         return F32
@@ -78,6 +83,8 @@ class Ops:
             "sb_attn_decode_balanced": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
                                         c_void_p],
             "sb_attn_decode": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
+            "sb_attn_decode_fused": [SbFusedQK, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
+                                     c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
                           c_void_p],
@@ -94,6 +101,7 @@ class Ops:
         self.use_stream = os.environ.get("STARTER_B200_STREAM", "1") != "0"  # the TMA + tcgen05 product for decode
         self._kernel_status = None
         self.decode_balanced = os.environ.get("STARTER_B200_ATTN", "balanced") != "split"
+        self.fuse_qk = os.environ.get("STARTER_B200_FUSE_QK", "1") != "0"
         self.prefill_tensor_memory = os.environ.get("STARTER_B200_PREFILL", "tc") != "mma"
 
     # ---- plumbing -----------------------------------------------------------------------
@@ -351,6 +359,53 @@ class Ops:
             self._scratch[key] = buf
         return buf
 
+    def _split_decode(self, ctx, kv, n_heads) -> bool:
+        """True when a step is served by the split-key decode kernel: one token per sequence, bfloat16 cache with head
+        size 64 or 128, at most 16 query heads per kv head, and no more (sequence, kv head) pairs than blocks fit at once."""
+        if kv.head_dim not in (64, 128) or n_heads % kv.n_kv_heads or n_heads // kv.n_kv_heads > 16:
+            return False
+        if not (ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs):
+            return False
+        pairs = ctx.n_seqs * kv.n_kv_heads
+        return not (self.decode_balanced and pairs > self.decode_resident(kv.head_dim) and ctx.n_seqs <= 1024)
+
+    def qk_attention(self, ctx, qkv, layer_cache, n_heads, n_kv_heads, head_dim, q_norm, k_norm, eps, rotary, scale, window):
+        """qk_norm_rope_store and attention in one kernel, for the steps that the split-key decode kernel serves and a
+        rotary encoding over the whole head (or none).  Returns None when the step is not of that kind: the caller then
+        makes the two calls."""
+        if not self.fuse_qk or qkv.dtype != torch.bfloat16 or layer_cache.group.k.dtype != torch.bfloat16:
+            return None
+        kv = self._kv(layer_cache)
+        if kv.head_dim != head_dim or (n_kv_heads and kv.n_kv_heads != n_kv_heads) or not self._split_decode(ctx, kv, n_heads):
+            return None
+        if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
+            raise KernelError("qk_attention: qkv has the wrong width")
+        cos = sin = None
+        if rotary is not None:
+            cos, sin, rotary_dim = rotary
+            if rotary_dim != head_dim or cos.dtype != torch.bfloat16:
+                return None
+            if cos.shape[1] * 2 != rotary_dim:
+                raise KernelError("qk_attention: rotary tables do not fit the run")
+            if cos.shape[0] < ctx.kv_bound:
+                raise KernelError(f"the rotary table covers {cos.shape[0]} positions, the step reaches {ctx.kv_bound}")
+        norm_f32 = 0
+        for w in (q_norm, k_norm):
+            if w is not None:
+                if w.dtype not in (torch.float32, torch.bfloat16):
+                    return None
+                norm_f32 = int(w.dtype == torch.float32)
+        if q_norm is not None and k_norm is not None and q_norm.dtype != k_norm.dtype:
+            return None
+        fused = SbFusedQK(_ptr(qkv), _ptr(q_norm), _ptr(k_norm), _ptr(cos), _ptr(sin), _ptr(ctx.status), float(eps), norm_f32,
+                          int(n_kv_heads > 0), 0)
+        out = torch.empty((qkv.shape[0], n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        n_splits = self.decode_splits(ctx.n_seqs, kv.n_kv_heads, layer_cache.group.table_width, kv.head_dim)
+        partial, counters = self._decode_scratch(qkv.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, n_splits)
+        self._check(self.lib.sb_attn_decode_fused(fused, _ptr(out), self._batch(ctx), kv, n_heads, scale, int(window or 0),
+                                                  n_splits, _ptr(partial), _ptr(counters), self._stream()), "attn_decode_fused")
+        return out
+
     def attention(self, ctx, q, layer_cache, n_heads, scale, window):
         """Causal attention of the step's rows over the layer's cache.  bfloat16 with head size 64 or
         128: the split-key decode kernel for steps of one token per sequence, the flash kernel for
@@ -363,9 +418,8 @@ class Ops:
             raise KernelError(f"{n_heads} query heads cannot share {kv.n_kv_heads} key/value heads evenly")
         if q.dtype == torch.bfloat16 and kv.head_dim in (64, 128):
             decode = ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs and n_heads // kv.n_kv_heads <= 16
-            pairs = ctx.n_seqs * kv.n_kv_heads
-            force = os.environ.get("STARTER_B200_ATTN") == "force_balanced"
-            if decode and self.decode_balanced and (pairs > self.decode_resident(kv.head_dim) or force) and ctx.n_seqs <= 1024:
+            split = decode and self._split_decode(ctx, kv, n_heads)
+            if decode and not split:
                 # More pairs than blocks fit at once: one block per SM, each with an equal share of all pages.
                 grid = min(self.sm_count(), 512)
                 key = ("attn_decode_balanced", q.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, grid)
@@ -378,7 +432,7 @@ class Ops:
                 self._check(self.lib.sb_attn_decode_balanced(_ptr(q), _ptr(out), self._batch(ctx), kv, n_heads, scale,
                                                              int(window or 0), grid, _ptr(buf[0]), _ptr(buf[1]),
                                                              self._stream()), "attn_decode_balanced")
-            elif decode:
+            elif split:
                 g = layer_cache.group
                 n_splits = self.decode_splits(ctx.n_seqs, kv.n_kv_heads, g.table_width, kv.head_dim)
                 partial, counters = self._decode_scratch(q.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, n_splits)

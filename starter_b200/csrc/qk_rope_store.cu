@@ -19,8 +19,10 @@ __global__ void qk_rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
                                      const W* __restrict__ k_norm_w, float eps, const T* __restrict__ cos_t,
                                      const T* __restrict__ sin_t, int rotary_dim, int* status) {
     __shared__ float y[QK_MAX_D];
+    sb_stamp(3, 0);
     pdl_wait();
     pdl_launch_dependents();   // the attention that follows looks up its pages and fetches old keys meanwhile
+    sb_stamp(3, 1);
     const int row = blockIdx.x, head = blockIdx.y, lane = threadIdx.x;
     const int D = kv.head_dim;
     const int width = (n_heads + 2 * n_kv_heads) * D;
@@ -74,6 +76,7 @@ __global__ void qk_rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
         }
         dst[d] = from_f<T>(o);
     }
+    sb_stamp(3, 2);
 }
 
 
@@ -189,3 +192,5 @@ extern "C" int sb_qk_rope_store(int dtype, int wdtype, const void* qkv, void* q_
 #undef SB_QK
     SB_LAUNCH_CHECK();
 }
+
+SB_TIMELINE_SETTER(rope)

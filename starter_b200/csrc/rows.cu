@@ -66,8 +66,10 @@ template <class W, bool ADD>
 __global__ void rmsnorm_vec_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfloat16* __restrict__ delta,
                                    const W* __restrict__ weight, __nv_bfloat16* __restrict__ out, int width, float eps) {
     __shared__ float red[33];
+    sb_stamp(1, 0);
     pdl_wait();
     pdl_launch_dependents();
+    sb_stamp(1, 1);
     const long long base = (long long)blockIdx.x * width;
     const int c = threadIdx.x * 8;
     const bool active = c < width;
@@ -114,6 +116,7 @@ __global__ void rmsnorm_vec_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfl
         }
         *reinterpret_cast<uint4*>(out + base + c) = res;
     }
+    sb_stamp(1, 2);
 }
 
 template <class T>
@@ -255,3 +258,5 @@ int sb_advance_lengths(SbBatch b, int* lengths, cudaStream_t stream) {
 const char* sb_error_string(int code) { return cudaGetErrorString((cudaError_t)code); }
 
 }  // extern "C"
+
+SB_TIMELINE_SETTER(rows)

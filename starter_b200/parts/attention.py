@@ -70,10 +70,16 @@ class Attention:
     def forward(self, ctx, h, layer_cache):
         qkv = self.ops.linear(h, self.w_qkv)
         rotary = self.position.fused_rotary() if self.position is not None else None
-        q = self.ops.qk_norm_rope_store(ctx, qkv, layer_cache, self.num_heads,
-                                        self.num_kv_heads if self.stores_kv else 0, self.head_dim,
-                                        self.q_norm, self.k_norm, self.norm_eps, rotary)
-        a = self.ops.attention(ctx, q, layer_cache, self.num_heads, self.scale, self.window)
+        n_kv = self.num_kv_heads if self.stores_kv else 0
+        a = None
+        one_call = getattr(self.ops, "qk_attention", None)   # optional: both steps in one kernel where the ops have it
+        if one_call is not None:
+            a = one_call(ctx, qkv, layer_cache, self.num_heads, n_kv, self.head_dim, self.q_norm, self.k_norm,
+                         self.norm_eps, rotary, self.scale, self.window)
+        if a is None:
+            q = self.ops.qk_norm_rope_store(ctx, qkv, layer_cache, self.num_heads, n_kv, self.head_dim,
+                                            self.q_norm, self.k_norm, self.norm_eps, rotary)
+            a = self.ops.attention(ctx, q, layer_cache, self.num_heads, self.scale, self.window)
         return self.ops.linear(a, self.w_o)
 
 

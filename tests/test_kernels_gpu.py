@@ -232,6 +232,58 @@ def test_decode_attention(ops, ref, monkeypatch, heads, kv_heads, head_dim, wind
         assert float((outs[0][-1, :head_dim].float() - want).abs().max()) < 0.05 * float(want.abs().max())
 
 
+@pytest.mark.parametrize("splits", [1, 3, 8, 11])
+@pytest.mark.parametrize("heads,kv_heads,head_dim,window,norm,rotary,store", [
+    (8, 2, 128, None, torch.bfloat16, True, True), (16, 1, 64, None, torch.float32, True, True),
+    (6, 3, 64, 100, None, True, True), (4, 4, 128, 700, torch.bfloat16, False, True),
+    (12, 2, 128, None, torch.bfloat16, True, False)])
+def test_decode_attention_with_preparation_inside(ops, ref, monkeypatch, heads, kv_heads, head_dim, window, norm, rotary,
+                                                  store, splits):
+    """The decode kernel that norms, rotates and stores q and k itself, against the two separate calls of the
+    torch restatement: the attention's output and what it left in the cache.  Lengths put the new token at
+    the start of a page, at its end, and in a sequence's first position."""
+    dtype = torch.bfloat16
+    monkeypatch.setattr(ops, "decode_balanced", False)
+    monkeypatch.setattr(ops, "decode_splits", lambda *a: splits)
+    cache = Cache([KVRequest(kv_heads, head_dim, window)], n_slots=6, max_tokens=64 * 60, dtype=dtype, device="cuda",
+                  max_seq_tokens=1600, max_step_tokens=64)
+    g = cache.groups[0]
+    g.k.copy_(rand(tuple(g.k.shape), dtype, 80))
+    g.v.copy_(rand(tuple(g.v.shape), dtype, 81))
+    lengths = [0, 63, 64, 700, 1500]
+    slots = [cache.alloc() for _ in lengths]
+    for s, n in zip(slots, lengths):
+        cache.assume_length(s, n)
+        cache.reserve(s, n + 1)
+    cache.flush()
+    ctx = make_ctx(cache, ops, slots, [1] * len(lengths), dtype)
+    n_kv = kv_heads if store else 0
+    qkv = rand((len(lengths), (heads + 2 * n_kv) * head_dim), dtype, 82)
+    q_w = k_w = None
+    if norm is not None:
+        q_w, k_w = 1.0 + rand((head_dim,), norm, 83, 0.2), 1.0 + rand((head_dim,), norm, 84, 0.2)
+    tables = None
+    if rotary:
+        angle = torch.arange(1600, dtype=torch.float32, device="cuda")[:, None] * \
+            (10000.0 ** (-torch.arange(head_dim // 2, dtype=torch.float32, device="cuda") * 2 / head_dim))[None, :]
+        tables = (angle.cos().to(dtype), angle.sin().to(dtype), head_dim)
+    scale = 1.0 / math.sqrt(head_dim)
+    k0, v0 = g.k.clone(), g.v.clone()
+    got = ops.qk_attention(ctx, qkv, cache.layers[0], heads, n_kv, head_dim, q_w, k_w, 1e-5, tables, scale, window)
+    assert got is not None, "the step is of the kind the fused kernel serves"
+    k_got, v_got = g.k.clone(), g.v.clone()
+    g.k.copy_(k0)
+    g.v.copy_(v0)
+    q = ref.qk_norm_rope_store(ctx, qkv, cache.layers[0], heads, n_kv, head_dim, q_w, k_w, 1e-5, tables)
+    want = ref.attention(ctx, q, cache.layers[0], heads, scale, window)
+    close(got, want, dtype, "decode attention with q/k preparation inside")
+    close(k_got, g.k, dtype, "keys left in the cache")
+    assert torch.equal(v_got, g.v)
+    assert int(ctx.status.item()) == 0
+    if not store:
+        assert torch.equal(k_got, k0)
+
+
 @pytest.mark.parametrize("M", [1, 5, 8, 11, 16])
 @pytest.mark.parametrize("splits,deep,warps", [(1, False, 8), (3, False, 8), (2, True, 8), (1, False, 4), (2, False, 4)])
 def test_skinny_product_variants(ops, ref, M, splits, deep, warps):

@@ -59,8 +59,9 @@ def test_no_alloc_entry_point_matches_the_ordinary_one():
     message.restype = ctypes.c_char_p
     stream = c_void_p(torch.cuda.current_stream().cuda_stream)
 
-    # two calls in a row, with different shapes and split counts, each against the ordinary entry point
-    for heads, kv_heads, head_dim, lengths, n_splits, seed in [(8, 2, 128, [700, 5, 64, 300], 5, 1),
+    # two calls in a row, with different shapes and split counts (12 splits go through the scratch, 3 merge in
+    # shared memory), each against the ordinary entry point
+    for heads, kv_heads, head_dim, lengths, n_splits, seed in [(8, 2, 128, [700, 5, 64, 300], 12, 1),
                                                                (4, 4, 64, [1000, 0, 129], 3, 2)]:
         keep, batch, kv, q = _setup(heads, kv_heads, head_dim, lengths, seed)
         n = len(lengths)
