@@ -336,8 +336,9 @@ class Ops:
         return self._sm_count
 
     def decode_resident(self, head_dim: int) -> int:
-        """Blocks of the split-key decode attention that the GPU holds at once (three per SM at head size 128)."""
-        return (3 if head_dim > 64 else 4) * self.sm_count()
+        """Blocks of the split-key decode attention that the GPU holds at once (two per SM at head size 128:
+        100 KB of shared memory each)."""
+        return (2 if head_dim > 64 else 4) * self.sm_count()
 
     def decode_splits(self, n_seqs: int, n_kv_heads: int, max_pages: int, head_dim: int = 128) -> int:
         """How many blocks share one (sequence, kv head).  Measured on a B200 at a context of 4,096: about
