@@ -145,4 +145,32 @@ static inline void sb_launch(void (*kernel)(Exp...), dim3 grid, dim3 block, size
     cudaLaunchKernelEx(&config, kernel, static_cast<Act&&>(args)...);
 }
 
+// The same with the blocks grouped into clusters of `cluster` blocks (a dimension of 0 or 1 = no grouping).
+template <typename... Exp, typename... Act>
+static inline void sb_launch_cluster(void (*kernel)(Exp...), dim3 grid, dim3 block, dim3 cluster, size_t smem, cudaStream_t stream,
+                                     Act&&... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attr[2];
+    int n = 0;
+    if (sb_pdl_flag) {
+        attr[n].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attr[n].val.programmaticStreamSerializationAllowed = 1;
+        ++n;
+    }
+    if (cluster.x * cluster.y * cluster.z > 1) {
+        attr[n].id = cudaLaunchAttributeClusterDimension;
+        attr[n].val.clusterDim.x = cluster.x;
+        attr[n].val.clusterDim.y = cluster.y;
+        attr[n].val.clusterDim.z = cluster.z;
+        ++n;
+    }
+    config.attrs = attr;
+    config.numAttrs = n;
+    cudaLaunchKernelEx(&config, kernel, static_cast<Act&&>(args)...);
+}
+
 #define SB_LAUNCH_CHECK() return (int)cudaGetLastError()

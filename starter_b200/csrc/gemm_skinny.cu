@@ -12,16 +12,22 @@
 //    same way;
 //  * a block owns 16 weight rows and one slice of K; its 8 warps walk the slice in turns of
 //    128 columns each and meet in shared memory at the end;
-//  * with several K slices per row block, partial sums go to scratch memory and the last block
-//    to arrive adds them (an atomic counter per row block), so the output is written once.
+//  * with 2 to 8 K slices per row block, the slices' blocks form a thread-block cluster and add their sums
+//    through one another's shared memory; with more, partial sums go to scratch memory and the last
+//    block to arrive adds them (an atomic counter per row block).  Either way the output is written once.
 // Optional fusions: the SwiGLU epilogue for a fused [gate; up] matrix (engine/kernels/gemm.py:
 // 116-168: both halves rounded to bfloat16, silu in 32-bit rounded, product rounded).
+#include <cooperative_groups.h>
+
 #include "common.cuh"
+
+namespace cg = cooperative_groups;
 
 #define GS_WARPS 8
 #define GS_ROWS 16          // weight rows per block
 #define GS_KWARP 128        // columns one warp covers per turn (4 blocks of 32)
 #define GS_KTURN (GS_WARPS * GS_KWARP)
+#define GS_MAX_CLUSTER 8    // K slices that meet through the cluster's shared memory
 
 __device__ __forceinline__ void mma_bf16_16816(float (&c)[4], unsigned int a0, unsigned int a1, unsigned int a2,
                                                unsigned int a3, unsigned int b0, unsigned int b1) {
@@ -48,11 +54,11 @@ __device__ __forceinline__ float silu_mul_bf16(float g, float u) {
 // take the gate rows of the block, warps 4-7 the matching up rows, and the output is swiglu(gate, up).
 // DEEP: a warp requests the next turn's weights before it multiplies the current turn (more bytes in flight
 // per warp, more registers, fewer resident blocks); worth it when few blocks share an SM.
-template <int NT, bool GATE_UP, bool DEEP, int WARPS>
+template <int NT, bool GATE_UP, bool DEEP, int WARPS, bool CLUSTER>
 __global__ void __launch_bounds__(WARPS * 32, DEEP ? 2 : (WARPS == 8 ? 4 : 8))
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, void* __restrict__ C,
-                   int M, int n_out, int K, int k_per_split, int n_splits, int out_f32, float* __restrict__ partial,
-                   int* __restrict__ counters) {
+                   int M, int n_out, int K, int k_per_split, int n_splits, int out_f32,
+                   float* __restrict__ partial, int* __restrict__ counters) {
     constexpr int GROUPS = GATE_UP ? 2 : 1;              // row groups the warps are divided into
     constexpr int WPG = WARPS / GROUPS;                  // warps per group, sharing K among them
     __shared__ float red[WARPS][GS_ROWS][8 * NT + 1];
@@ -151,11 +157,38 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
         float v = 0.f;
 #pragma unroll
         for (int w = 0; w < WPG; ++w) v += red[grp * WPG + w][r][m];
-        if (n_splits > 1) {
+        if (n_splits > 1 && !CLUSTER) {
             my_part[e] = v;
         } else {
-            red[grp * WPG][r][m] = v;  // keep the block's sums for the epilogue
+            red[grp * WPG][r][m] = v;  // keep the block's sums for the epilogue (or for the cluster)
         }
+    }
+    if (CLUSTER) {
+        // The blocks of this row block's K slices are one cluster (rank = slice).  Each finishes an equal share of
+        // the outputs from the sums in all the blocks' shared memory, added in the order of the slices.
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        constexpr int OUTS = GS_ROWS * 8 * NT;
+        const int share = (OUTS + n_splits - 1) / n_splits;
+        const int e_end = min(OUTS, (split + 1) * share);
+        for (int e = split * share + tid; e < e_end; e += WARPS * 32) {
+            const int r = e % GS_ROWS, m = e / GS_ROWS;
+            if (m >= M || n0 + r >= n_out) continue;
+            float v = 0.f, v2 = 0.f;
+            for (int c = 0; c < n_splits; ++c) {
+                v += *cluster.map_shared_rank(&red[0][r][m], c);
+                if (GATE_UP) v2 += *cluster.map_shared_rank(&red[WPG][r][m], c);
+            }
+            if (GATE_UP) v = silu_mul_bf16(v, v2);
+            const long long o = (long long)m * n_out + n0 + r;
+            if (out_f32)
+                reinterpret_cast<float*>(C)[o] = v;
+            else
+                reinterpret_cast<__nv_bfloat16*>(C)[o] = __float2bfloat16_rn(v);
+        }
+        cluster.sync();   // nobody leaves while its sums are still being read
+        sb_stamp(2, 2);
+        return;
     }
     if (n_splits > 1) {
         __threadfence();
@@ -210,19 +243,28 @@ int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int 
         (long long)k_per_split * n_splits < K || (warps != 4 && warps != 8))
         return (int)cudaErrorInvalidValue;
     dim3 grid((n_out + GS_ROWS - 1) / GS_ROWS, n_splits);
+    const int cluster_reduce = n_splits >= 2 && n_splits <= GS_MAX_CLUSTER;
+    dim3 cluster(1, cluster_reduce ? n_splits : 1, 1);
     const __nv_bfloat16* a = (const __nv_bfloat16*)A;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
-#define SB_SKINNY(NT, GU)                                                                                              \
+#define SB_SKINNY_(NT, GU, CL)                                                                                            \
     do {                                                                                                               \
         if (deep)                                                                                                      \
-            sb_launch(gemm_skinny_kernel<NT, GU, true, 8>, grid, 256, 0, stream, a, w, C, M, n_out, K, k_per_split,     \
-                      n_splits, out_f32, partial, counters);                                                           \
+            sb_launch_cluster(gemm_skinny_kernel<NT, GU, true, 8, CL>, grid, 256, cluster, 0, stream, a, w, C, M, n_out, K,  \
+                              k_per_split, n_splits, out_f32, partial, counters);                                          \
         else if (warps == 4)                                                                                           \
-            sb_launch(gemm_skinny_kernel<NT, GU, false, 4>, grid, 128, 0, stream, a, w, C, M, n_out, K, k_per_split,    \
-                      n_splits, out_f32, partial, counters);                                                           \
+            sb_launch_cluster(gemm_skinny_kernel<NT, GU, false, 4, CL>, grid, 128, cluster, 0, stream, a, w, C, M, n_out, K, \
+                              k_per_split, n_splits, out_f32, partial, counters);                                          \
         else                                                                                                           \
-            sb_launch(gemm_skinny_kernel<NT, GU, false, 8>, grid, 256, 0, stream, a, w, C, M, n_out, K, k_per_split,    \
-                      n_splits, out_f32, partial, counters);                                                           \
+            sb_launch_cluster(gemm_skinny_kernel<NT, GU, false, 8, CL>, grid, 256, cluster, 0, stream, a, w, C, M, n_out, K, \
+                              k_per_split, n_splits, out_f32, partial, counters);                                          \
+    } while (0)
+#define SB_SKINNY(NT, GU)                        \
+    do {                                         \
+        if (cluster_reduce)                      \
+            SB_SKINNY_(NT, GU, true);            \
+        else                                     \
+            SB_SKINNY_(NT, GU, false);           \
     } while (0)
     if (M <= 8) {
         if (gate_up) SB_SKINNY(1, true); else SB_SKINNY(1, false);
@@ -230,6 +272,7 @@ int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int 
         if (gate_up) SB_SKINNY(2, true); else SB_SKINNY(2, false);
     }
 #undef SB_SKINNY
+#undef SB_SKINNY_
     SB_LAUNCH_CHECK();
 }
 

@@ -285,7 +285,7 @@ def test_decode_attention_with_preparation_inside(ops, ref, monkeypatch, heads, 
 
 
 @pytest.mark.parametrize("M", [1, 5, 8, 11, 16])
-@pytest.mark.parametrize("splits,deep,warps", [(1, False, 8), (3, False, 8), (2, True, 8), (1, False, 4), (2, False, 4)])
+@pytest.mark.parametrize("splits,deep,warps", [(1, False, 8), (3, False, 8), (2, True, 8), (1, False, 4), (2, False, 4), (8, False, 4), (11, False, 8)])
 def test_skinny_product_variants(ops, ref, M, splits, deep, warps):
     """The weight-streaming product with every row tile, K slicing and pipelining variant, with and
     without the SwiGLU epilogue, at sizes that are no multiples of its tiles."""
