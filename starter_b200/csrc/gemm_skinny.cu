@@ -50,12 +50,14 @@ __device__ __forceinline__ float silu_mul_bf16(float g, float u) {
     return s * ub;
 }
 
-// NT: activation tiles of 8 rows (M <= 8 * NT).  GATE_UP: W is [2 * n_out, K], gate rows first; warps 0-3
-// take the gate rows of the block, warps 4-7 the matching up rows, and the output is swiglu(gate, up).
-// DEEP: a warp requests the next turn's weights before it multiplies the current turn (more bytes in flight
-// per warp, more registers, fewer resident blocks); worth it when few blocks share an SM.
-template <int NT, bool GATE_UP, bool DEEP, int WARPS, bool CLUSTER>
-__global__ void __launch_bounds__(WARPS * 32, DEEP ? 2 : (WARPS == 8 ? 4 : 8))
+// NT: activation tiles of 8 rows (M <= 8 * NT).  GATE_UP: W is [2 * n_out, K], gate rows first; the first half of
+// the warps takes the gate rows of the block, the second half the matching up rows, and the output is swiglu(gate, up).
+// TILED: W is the tile-major copy that sb_tile_matrix makes: [row tile of 16][turn of 128 columns][16 rows][128
+// columns], rows and columns zero-padded to whole tiles (with GATE_UP: the gate half's tiles, then the up half's).
+// What a warp reads in one turn is then one contiguous piece of 4 KB instead of sixteen pieces of 256 bytes a row
+// apart, which memory serves faster (measured on the 4B shapes: the decode step 3.7% shorter at batch 8, 6.8% at batch 1).
+template <int NT, bool GATE_UP, bool TILED, int WARPS, bool CLUSTER>
+__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 4 : 8)
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, void* __restrict__ C,
                    int M, int n_out, int K, int k_per_split, int n_splits, int out_f32,
                    float* __restrict__ partial, int* __restrict__ counters) {
@@ -73,6 +75,9 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     const bool ok_lo = n0 + g < n_out, ok_hi = n0 + g + 8 < n_out;
     const __nv_bfloat16* w_lo = W + row_lo * K;
     const __nv_bfloat16* w_hi = W + row_hi * K;
+    // TILED: this lane's place in the first turn of the block's row tile (see the layout at the top of the file)
+    const __nv_bfloat16* w_tile = W + ((long long)group * gridDim.x + blockIdx.x) * ((K + GS_KWARP - 1) / GS_KWARP) * (GS_ROWS * GS_KWARP) +
+                                  g * GS_KWARP + c * 8;
 
     float acc[NT][4];
 #pragma unroll
@@ -82,12 +87,21 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     // The weights of the next turn are requested before the current turn is multiplied, so that a
     // warp always has a turn's worth of loads (4 KB) in flight behind the one it works on.
     auto load_w = [&](uint4 (&lo)[4], uint4 (&hi)[4], int kt) {
+        if (TILED) {   // whole turns exist, zero-padded: no edges; the turn is 4 KB in one piece
+            const __nv_bfloat16* wt = w_tile + (long long)(kt / GS_KWARP) * (GS_ROWS * GS_KWARP);
 #pragma unroll
-        for (int u = 0; u < 4; ++u) {
-            const int k = kt + u * 32 + c * 8;
-            const bool ok = k < k_end;
-            lo[u] = ok && ok_lo ? load_stream(w_lo + k) : zero;
-            hi[u] = ok && ok_hi ? load_stream(w_hi + k) : zero;
+            for (int u = 0; u < 4; ++u) {
+                lo[u] = load_stream(wt + u * 32);
+                hi[u] = load_stream(wt + 8 * GS_KWARP + u * 32);
+            }
+        } else {
+#pragma unroll
+            for (int u = 0; u < 4; ++u) {
+                const int k = kt + u * 32 + c * 8;
+                const bool ok = k < k_end;
+                lo[u] = ok && ok_lo ? load_stream(w_lo + k) : zero;
+                hi[u] = ok && ok_hi ? load_stream(w_hi + k) : zero;
+            }
         }
     };
     auto turn = [&](const uint4 (&lo)[4], const uint4 (&hi)[4], int kt) {
@@ -111,30 +125,16 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     constexpr int STRIDE = WPG * GS_KWARP;
     int kt = k_begin + wk * GS_KWARP;
     sb_stamp(2, 0);
-    if (DEEP) {
-        uint4 lo_a[4], hi_a[4], lo_b[4], hi_b[4];
-        if (kt < k_end) load_w(lo_a, hi_a, kt);
+    // The weights do not depend on the kernel before this one: a turn's weights are requested
+    // before the wait for that kernel (which matters in the first turn only), the activations after it.
+#pragma unroll 1
+    for (; kt < k_end; kt += STRIDE) {
+        uint4 lo[4], hi[4];
+        load_w(lo, hi, kt);
         pdl_wait();
-        while (kt < k_end) {
-            if (kt + STRIDE < k_end) load_w(lo_b, hi_b, kt + STRIDE);
-            turn(lo_a, hi_a, kt);
-            kt += STRIDE;
-            if (kt >= k_end) break;
-            if (kt + STRIDE < k_end) load_w(lo_a, hi_a, kt + STRIDE);
-            turn(lo_b, hi_b, kt);
-            kt += STRIDE;
-        }
-    } else {
-        // The weights do not depend on the kernel before this one: a turn's weights are requested
-        // before the wait for that kernel (which matters in the first turn only), the activations after it.
-        for (; kt < k_end; kt += STRIDE) {
-            uint4 lo[4], hi[4];
-            load_w(lo, hi, kt);
-            pdl_wait();
-            turn(lo, hi, kt);
-        }
-        pdl_wait();   // a warp without a turn of its own waits too, before anything is written
+        turn(lo, hi, kt);
     }
+    pdl_wait();   // a warp without a turn of its own waits too, before anything is written
 
     sb_stamp(2, 1);
     pdl_launch_dependents();   // the weights are read; the next kernel may start fetching its own
@@ -224,6 +224,24 @@ gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __r
     sb_stamp(2, 2);
 }
 
+// dst element index -> (half, row tile, turn, row in tile, column in turn); 8 elements (16 bytes) per thread.
+__global__ void tile_matrix_kernel(const __nv_bfloat16* __restrict__ src, __nv_bfloat16* __restrict__ dst, int rows, int K,
+                                   int halves, long long total) {
+    const int kt_n = (K + GS_KWARP - 1) / GS_KWARP, rt_n = (rows + GS_ROWS - 1) / GS_ROWS;
+    for (long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 8; i < total; i += (long long)gridDim.x * blockDim.x * 8) {
+        const int col = (int)(i % GS_KWARP);
+        const int r_in = (int)((i / GS_KWARP) % GS_ROWS);
+        const long long tile = i / (GS_ROWS * GS_KWARP);
+        const int kt = (int)(tile % kt_n);
+        const int rt = (int)((tile / kt_n) % rt_n);
+        const int half = (int)(tile / ((long long)kt_n * rt_n));
+        const int row = rt * GS_ROWS + r_in, k = kt * GS_KWARP + col;
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (row < rows && k < K) v = *reinterpret_cast<const uint4*>(src + ((long long)half * rows + row) * K + k);   // K % 8 == 0
+        *reinterpret_cast<uint4*>(dst + i) = v;
+    }
+}
+
 extern "C" {
 
 // Scratch for n_splits > 1: partial sums (floats) and one counter per row block (ints, zero before
@@ -235,9 +253,9 @@ long long sb_gemm_skinny_scratch_floats(int M, int n_out, int n_splits, int gate
 }
 
 // A [M, K], W [n_out, K] (or [2 * n_out, K] with gate_up), C [M, n_out] bfloat16 or float.
-// Takes M <= 16 and K a multiple of 8; k_per_split a multiple of 128.
+// Takes M <= 16 and K a multiple of 8; k_per_split a multiple of 128.  tiled: W is the tile-major copy (see above).
 int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int K, int n_splits, int k_per_split,
-                   int gate_up, int out_f32, int deep, int warps, float* partial, int* counters, cudaStream_t stream) {
+                   int gate_up, int out_f32, int tiled, int warps, float* partial, int* counters, cudaStream_t stream) {
     if (M <= 0 || n_out <= 0) return 0;
     if (M > 16 || (K & 7) || n_splits < 1 || n_splits > 65535 || (k_per_split % GS_KWARP) ||
         (long long)k_per_split * n_splits < K || (warps != 4 && warps != 8))
@@ -247,24 +265,22 @@ int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int 
     dim3 cluster(1, cluster_reduce ? n_splits : 1, 1);
     const __nv_bfloat16* a = (const __nv_bfloat16*)A;
     const __nv_bfloat16* w = (const __nv_bfloat16*)W;
-#define SB_SKINNY_(NT, GU, CL)                                                                                            \
+#define SB_SKINNY3(NT, GU, TL, CL)                                                                                     \
     do {                                                                                                               \
-        if (deep)                                                                                                      \
-            sb_launch_cluster(gemm_skinny_kernel<NT, GU, true, 8, CL>, grid, 256, cluster, 0, stream, a, w, C, M, n_out, K,  \
-                              k_per_split, n_splits, out_f32, partial, counters);                                          \
-        else if (warps == 4)                                                                                           \
-            sb_launch_cluster(gemm_skinny_kernel<NT, GU, false, 4, CL>, grid, 128, cluster, 0, stream, a, w, C, M, n_out, K, \
-                              k_per_split, n_splits, out_f32, partial, counters);                                          \
+        if (warps == 4)                                                                                                \
+            sb_launch_cluster(gemm_skinny_kernel<NT, GU, TL, 4, CL>, grid, 128, cluster, 0, stream, a, w, C, M, n_out, K, \
+                              k_per_split, n_splits, out_f32, partial, counters);                                      \
         else                                                                                                           \
-            sb_launch_cluster(gemm_skinny_kernel<NT, GU, false, 8, CL>, grid, 256, cluster, 0, stream, a, w, C, M, n_out, K, \
-                              k_per_split, n_splits, out_f32, partial, counters);                                          \
+            sb_launch_cluster(gemm_skinny_kernel<NT, GU, TL, 8, CL>, grid, 256, cluster, 0, stream, a, w, C, M, n_out, K, \
+                              k_per_split, n_splits, out_f32, partial, counters);                                      \
     } while (0)
-#define SB_SKINNY(NT, GU)                        \
-    do {                                         \
-        if (cluster_reduce)                      \
-            SB_SKINNY_(NT, GU, true);            \
-        else                                     \
-            SB_SKINNY_(NT, GU, false);           \
+#define SB_SKINNY2(NT, GU, TL)                                                  \
+    do {                                                                        \
+        if (cluster_reduce) SB_SKINNY3(NT, GU, TL, true); else SB_SKINNY3(NT, GU, TL, false); \
+    } while (0)
+#define SB_SKINNY(NT, GU)                                                       \
+    do {                                                                        \
+        if (tiled) SB_SKINNY2(NT, GU, true); else SB_SKINNY2(NT, GU, false);    \
     } while (0)
     if (M <= 8) {
         if (gate_up) SB_SKINNY(1, true); else SB_SKINNY(1, false);
@@ -272,7 +288,22 @@ int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int 
         if (gate_up) SB_SKINNY(2, true); else SB_SKINNY(2, false);
     }
 #undef SB_SKINNY
-#undef SB_SKINNY_
+#undef SB_SKINNY2
+#undef SB_SKINNY3
+    SB_LAUNCH_CHECK();
+}
+
+// The tile-major copy of a row-major matrix for the kernel above.  src [halves * rows, K] bfloat16 row-major; dst
+// holds halves * ceil(rows / 16) * ceil(K / 128) tiles of 16 x 128 (sb_tile_matrix_elements of them in all).
+long long sb_tile_matrix_elements(int rows, int K, int halves) {
+    return (long long)halves * ((rows + GS_ROWS - 1) / GS_ROWS) * ((K + GS_KWARP - 1) / GS_KWARP) * (GS_ROWS * GS_KWARP);
+}
+
+int sb_tile_matrix(const void* src, void* dst, int rows, int K, int halves, cudaStream_t stream) {
+    if (rows <= 0 || K <= 0 || halves < 1) return (int)cudaErrorInvalidValue;
+    const long long total = sb_tile_matrix_elements(rows, K, halves);
+    const int blocks = (int)((total / 8 + 255) / 256 < 65535 * 16 ? (total / 8 + 255) / 256 : 65535 * 16);
+    tile_matrix_kernel<<<blocks, 256, 0, stream>>>((const __nv_bfloat16*)src, (__nv_bfloat16*)dst, rows, K, halves, total);
     SB_LAUNCH_CHECK();
 }
 

@@ -50,6 +50,8 @@ def bench_product(ops, kernel: str, shape: str, rows: int, copies: int):
     copies = min(copies, max(2, (1 << 31) // (w_rows * K * 2)))
     ws = [torch.randn(w_rows, K, device="cuda", dtype=torch.bfloat16) * 0.02 for _ in range(copies)]
     a = torch.randn(rows, K, device="cuda", dtype=torch.bfloat16)
+    if kernel == "skinny":   # as the parts do it: the decode product reads the tile-major copy when there is one
+        ws = [ops.prepare_matrix(w, halves=2 if gate_up else 1) for w in ws]
     if kernel == "stream":
         calls = [lambda w=w: ops._stream_product(a, w, n_out, gate_up, False) for w in ws]
     elif kernel == "skinny":

@@ -11,8 +11,9 @@ the compiled library, ``get_ops`` raises.
 from __future__ import annotations
 
 import ctypes
+import weakref
 import os
-from ctypes import POINTER, Structure, c_float, c_int, c_ulonglong, c_void_p
+from ctypes import POINTER, Structure, c_float, c_int, c_longlong, c_ulonglong, c_void_p
 
 import torch
 
@@ -62,6 +63,8 @@ class Ops:
         self.lib = lib
         self.launches = 0  # kernels of this library launched so far (cuBLAS calls are not counted)
         lib.sb_error_string.restype = ctypes.c_char_p
+        lib.sb_tile_matrix_elements.restype = c_longlong
+        lib.sb_tile_matrix_elements.argtypes = [c_int, c_int, c_int]
         lib.sb_error_string.argtypes = [c_int]
         sig = {
             "sb_embed": [c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p],
@@ -75,6 +78,7 @@ class Ops:
             "sb_attention_general": [c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_void_p],
             "sb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
                                c_void_p, c_void_p, c_void_p],
+            "sb_tile_matrix": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
             "sb_gemm_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                c_void_p, c_void_p],
             "sb_gemm_stream_plan": [c_int, c_int, c_int, POINTER(c_int), POINTER(c_int), POINTER(c_int)],
@@ -97,7 +101,9 @@ class Ops:
         lib.sb_set_pdl.restype = None
         self._scratch = {}
         self._sm_count = None
-        self.force_skinny = None  # (K slices, deep) for tuning runs; None = the rules below
+        self.force_skinny = None  # (K slices, tiled, warps) for tests and tuning runs; None = the rules below
+        self._tiled_bytes = 0     # bytes of tile-major copies alive (a copy hangs on its matrix as ._sb_tiled = (copy, halves))
+        self.decode_copy = os.environ.get("STARTER_B200_DECODE_COPY", "auto")   # "1", "0" or "auto"
         self.use_stream = os.environ.get("STARTER_B200_STREAM", "1") != "0"  # the TMA + tcgen05 product for decode
         self._kernel_status = None
         self.decode_balanced = os.environ.get("STARTER_B200_ATTN", "balanced") != "split"
@@ -139,12 +145,35 @@ class Ops:
         one before it in the stream is finishing; see common.cuh."""
         self.lib.sb_set_pdl(int(bool(on)))
 
-    def prepare_matrix(self, w: torch.Tensor) -> torch.Tensor:
-        """A weight matrix [out, in] as the products want it: contiguous, in the run's dtype."""
+    DECODE_COPY_SHARE = 0.2   # "auto": tile-major copies are made while they stay below this share of the device's memory
+
+    def _forget_copy(self, nbytes: int) -> None:
+        self._tiled_bytes -= nbytes
+
+    def prepare_matrix(self, w: torch.Tensor, halves: int = 1) -> torch.Tensor:
+        """A weight matrix [out, in] as the products want it: contiguous, in the run's dtype.  ``halves``: 2 for
+        a fused [gate; up] matrix (linear_swiglu pairs row r of the first half with row r of the second).
+
+        For bfloat16 matrices a second, tile-major copy is kept for the decode product (gemm_skinny.cu: one
+        contiguous piece per warp and turn instead of sixteen short ones; 4-7% of a decode step on the 4B
+        shapes), as long as all such copies together stay below DECODE_COPY_SHARE of the device's memory
+        (STARTER_B200_DECODE_COPY=1 always, =0 never).  Products with many rows read the row-major matrix."""
         if w.dim() != 2:
             raise KernelError(f"a weight matrix has two axes, got shape {tuple(w.shape)}")
         _code(w.dtype)
-        return w.contiguous()
+        w = w.contiguous()
+        if (w.is_cuda and w.dtype == torch.bfloat16 and w.shape[1] % 8 == 0 and w.shape[0] % halves == 0
+                and self.decode_copy != "0" and getattr(w, "_sb_tiled", None) is None):
+            rows = w.shape[0] // halves
+            n = self.lib.sb_tile_matrix_elements(rows, w.shape[1], halves)
+            total = torch.cuda.get_device_properties(w.device).total_memory
+            if self.decode_copy == "1" or self._tiled_bytes + 2 * n <= self.DECODE_COPY_SHARE * total:
+                tiled = torch.empty(n, dtype=torch.bfloat16, device=w.device)
+                self._check(self.lib.sb_tile_matrix(_ptr(w), _ptr(tiled), rows, w.shape[1], halves, self._stream()), "tile_matrix")
+                w._sb_tiled = (tiled, halves)   # lives and dies with the matrix object that the parts hold
+                self._tiled_bytes += 2 * n
+                weakref.finalize(w, self._forget_copy, 2 * n)
+        return w
 
     # ---- rows ---------------------------------------------------------------------------
 
@@ -264,11 +293,14 @@ class Ops:
                    torch.zeros(blocks, dtype=torch.int32, device=a.device))
             self._scratch[key] = buf
         out = torch.empty((M, n_out), dtype=torch.float32 if out_float32 else torch.bfloat16, device=a.device)
-        deep = False if self.force_skinny is None else self.force_skinny[1]
         warps = self.skinny_warps(blocks * n_splits) if self.force_skinny is None or len(self.force_skinny) < 3 else self.force_skinny[2]
-        self._check(self.lib.sb_gemm_skinny(_ptr(a), _ptr(w), _ptr(out), M, n_out, K, n_splits, k_per_split, int(gate_up),
-                                            int(out_float32), int(deep), warps, _ptr(buf[0]), _ptr(buf[1]), self._stream()),
-                    "gemm_skinny")
+        copy = getattr(w, "_sb_tiled", None)
+        if copy is not None and (copy[1] != (2 if gate_up else 1) or (self.force_skinny is not None and not self.force_skinny[1])):
+            copy = None   # tiled for the other pairing of rows, or a test asks for the row-major path
+        src = copy[0] if copy is not None else w
+        self._check(self.lib.sb_gemm_skinny(_ptr(a), _ptr(src), _ptr(out), M, n_out, K, n_splits, k_per_split, int(gate_up),
+                                            int(out_float32), int(copy is not None), warps, _ptr(buf[0]), _ptr(buf[1]),
+                                            self._stream()), "gemm_skinny")
         return out
 
     def linear(self, a, w, out_float32=False):

@@ -27,7 +27,7 @@ class GatedMLP:
         self.hidden_size = spec.hidden_size
         self.intermediate_size = spec.intermediate_size
         self.ops = runtime.ops
-        self.w_gate_up = self.ops.prepare_matrix(torch.cat([weights["gate"], weights["up"]], dim=0))
+        self.w_gate_up = self.ops.prepare_matrix(torch.cat([weights["gate"], weights["up"]], dim=0), halves=2)
         self.w_down = self.ops.prepare_matrix(weights["down"])
 
     def prepare(self, cache) -> None:

@@ -23,7 +23,7 @@ def _rnd(t, dtype):
 class EmulatedOps:
     name = "emulated"
 
-    def prepare_matrix(self, w):
+    def prepare_matrix(self, w, halves=1):
         return w
 
     # ---- rows ---------------------------------------------------------------------------

@@ -285,14 +285,21 @@ def test_decode_attention_with_preparation_inside(ops, ref, monkeypatch, heads, 
 
 
 @pytest.mark.parametrize("M", [1, 5, 8, 11, 16])
-@pytest.mark.parametrize("splits,deep,warps", [(1, False, 8), (3, False, 8), (2, True, 8), (1, False, 4), (2, False, 4), (8, False, 4), (11, False, 8)])
-def test_skinny_product_variants(ops, ref, M, splits, deep, warps):
-    """The weight-streaming product with every row tile, K slicing and pipelining variant, with and
-    without the SwiGLU epilogue, at sizes that are no multiples of its tiles."""
+@pytest.mark.parametrize("splits,tiled,warps", [(1, False, 8), (3, False, 8), (2, True, 8), (1, True, 4), (2, False, 4), (8, False, 4),
+                                                (11, False, 8), (3, True, 8), (11, True, 4)])
+def test_skinny_product_variants(ops, ref, M, splits, tiled, warps):
+    """The weight-streaming product with every row tile, K slicing, way of meeting (cluster, scratch) and weight
+    layout (row-major, tile-major copy), with and without the SwiGLU epilogue, at sizes that are no multiples
+    of its tiles."""
     dtype = torch.bfloat16
     try:
-        ops.force_skinny = (splits, deep, warps)
+        ops.force_skinny = (splits, tiled, warps)
         a, w = rand((M, 4104), dtype, 70), rand((2 * 1000, 4104), dtype, 71, 0.05)
+        if tiled:   # a copy for each pairing of rows: the whole matrix as one, and as [gate; up]
+            w_pairs = w.clone()
+            assert ops.prepare_matrix(w) is w and ops.prepare_matrix(w_pairs, halves=2) is w_pairs
+            assert w._sb_tiled[1] == 1 and w_pairs._sb_tiled[1] == 2
+            close(ops._skinny(a, w_pairs, 1000, True, False), ref.linear_swiglu(a, w), dtype, "skinny + swiglu, tile-major")
         close(ops._skinny(a, w, 2000, False, False), ref.linear(a, w), dtype, "skinny")
         close(ops._skinny(a, w, 2000, False, True), ref.linear(a, w, out_float32=True), dtype, "skinny, 32-bit out", rel=2e-3)
         close(ops._skinny(a, w, 1000, True, False), ref.linear_swiglu(a, w), dtype, "skinny + swiglu")
