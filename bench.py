@@ -288,7 +288,8 @@ def main() -> int:
                    "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
                    "tied": cfg.tie_word_embeddings, "global_batch": args.batch, "seq_len": args.context,
                    "prefill_tokens": T, "parallelism": "single GPU", "cuda_graphs": True,
-                   "l2": "each step reads all weights (larger than L2)", "peaks": peak_source},
+                   "l2": "each step reads all weights (larger than L2)", "peaks": peak_source,
+                   "decode_weight_copy_gb": round(getattr(ops, "_tiled_bytes", 0) / 1e9, 2)},
         "e2e": e2e,
         "prefill": {"value": round(T * 1000.0 / prefill_ms, 1), "tokens": T, "ms": round(prefill_ms, 3),
                     "frac": round(prefill_frac, 4)},
