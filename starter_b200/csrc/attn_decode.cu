@@ -271,7 +271,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
             float sum = 0.f;
 #pragma unroll
             for (int e = 0; e < 4; ++e) {
-                t[h][e] = exp2f(t[h][e] - m_safe);
+                t[h][e] = fast_exp2(t[h][e] - m_safe);
                 sum += t[h][e];
             }
             l[h] = l[h] * alpha[h] + sum;

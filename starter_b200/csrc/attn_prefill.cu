@@ -160,10 +160,10 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
             float sum[2] = {0.f, 0.f};
 #pragma unroll
             for (int nt = 0; nt < SB_PAGE / 8; ++nt) {
-                s[nt][0] = exp2f(s[nt][0] - m_safe[0]);
-                s[nt][1] = exp2f(s[nt][1] - m_safe[0]);
-                s[nt][2] = exp2f(s[nt][2] - m_safe[1]);
-                s[nt][3] = exp2f(s[nt][3] - m_safe[1]);
+                s[nt][0] = fast_exp2(s[nt][0] - m_safe[0]);
+                s[nt][1] = fast_exp2(s[nt][1] - m_safe[0]);
+                s[nt][2] = fast_exp2(s[nt][2] - m_safe[1]);
+                s[nt][3] = fast_exp2(s[nt][3] - m_safe[1]);
                 sum[0] += s[nt][0] + s[nt][1];
                 sum[1] += s[nt][2] + s[nt][3];
             }

@@ -14,10 +14,16 @@
 //   thread 0 issues  O_page[128 x 128] = P[128 x 64] V       (4 tcgen05.mma; V as it lies in the cache,
 //                                                             [key][d], is the MN-major form of that operand)
 //   every thread reads its row of O_page and folds it into its 128 accumulators: acc = acc * alpha + O_page.
-// Keys and values of the next page arrive by TMA while the current page is worked on.  Two blocks share an
-// SM (112 KB of shared memory and 256 columns of tensor memory each), so one block's softmax overlaps the
-// other's products.  Every wait on an mbarrier is bounded; on a time-out the block raises
-// SB_STATUS_TIMEOUT, leaves its loop at the next block-wide barrier and frees its tensor memory.
+// Who does what.  Warps 0-3 own the rows (softmax).  One thread of a fifth warp issues every TMA copy and every
+// tcgen05.mma and nothing else: issuing a product takes about as long as the tensor core needs for it (measured:
+// 840 cycles for S, 820 for O += P V), and a thread that also owned a row made its whole block wait for that.
+// The products run ahead of the softmax: S of page i + 1 goes into the second of two S buffers in tensor memory
+// while the rows work on page i, and O += P V of page i runs while they start on page i + 1.  Keys arrive two
+// pages ahead and values one page ahead, in two stages each.  The rows and the issuer meet only through
+// mbarriers (S ready, O done, P written); there is no block-wide barrier inside the loop.  Two blocks share an SM
+// (113 KB of shared memory and 256 columns of tensor memory each).  Every wait on an mbarrier is bounded; on a time-out the block raises
+// SB_STATUS_TIMEOUT and a flag in shared memory that ends every other wait of the block, which then frees its
+// tensor memory and returns.
 #include <cuda.h>
 
 #include <mutex>
@@ -29,6 +35,7 @@
 #define PT_D 128
 #define PT_WAIT_LIMIT (1ll << 31)
 #define PT_IDS 128
+#define PT_THREADS 160   // four warps of rows and the issuer's warp
 
 namespace {
 
@@ -38,6 +45,9 @@ __device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
@@ -122,7 +132,7 @@ __device__ __forceinline__ uint32_t idesc(int n, int b_mn_major) {
 
 }  // namespace
 
-__global__ void __launch_bounds__(128, 2)
+__global__ void __launch_bounds__(PT_THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
                        const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, SbBatch batch, SbKV kv,
                        int n_heads, float scale_log2, int window, int* status) {
@@ -135,10 +145,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     unsigned char* v_s = k_s + 2 * STAGE;          // [2 stages][2 blocks of [64][64]]
     unsigned char* p_s = v_s + 2 * STAGE;          // [128][64] probabilities
     uint64_t* bars = (uint64_t*)(p_s + PT_ROWS * 128);
-    uint64_t* kv_full = bars;                      // [2]
-    uint64_t* s_done = bars + 2;
-    uint64_t* o_done = bars + 3;
-    uint32_t* tmem_slot = (uint32_t*)(bars + 4);
+    uint64_t* k_full = bars;                       // [2] keys of a page have landed in stage i & 1
+    uint64_t* v_full = bars + 2;                   // [2] values likewise
+    uint64_t* s_done = bars + 4;                   // [2] S of page i is in S buffer i & 1 (and every product issued before it is done)
+    uint64_t* o_done = bars + 6;                   // [2] O += P V of page i is done
+    uint64_t* p_ready = bars + 8;                  // every row has read S of page i and written its P (128 arrivals)
+    uint32_t* tmem_slot = (uint32_t*)(bars + 9);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     int* s_pages = (int*)(tmem_slot + 4);          // [PT_IDS] ids of the block's next pages
     pdl_wait();
@@ -165,7 +177,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int n_pages = last_page - first_page + 1;
 
     if (tid == 0) {
-        mbar_init(&kv_full[0], 1); mbar_init(&kv_full[1], 1); mbar_init(s_done, 1); mbar_init(o_done, 1);
+#pragma unroll
+        for (int b = 0; b < 8; ++b) mbar_init(&bars[b], 1);
+        mbar_init(p_ready, PT_ROWS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -174,10 +188,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     // This thread's query row into shared memory, in the swizzled K-major layout the tensor core reads.
+    const bool owns_row = tid < PT_ROWS;
     const int t = t0 + tid;
     const int pos = t < total ? start + t / G : -1;
     const int lo = window > 0 ? max(0, pos - window + 1) : 0;
-    {
+    if (owns_row) {
         const __nv_bfloat16* src = q + ((long long)(row0 + (t < total ? t / G : 0)) * n_heads + kvh * G + (t < total ? t % G : 0)) * PT_D;
 #pragma unroll
         for (int c = 0; c < 16; ++c) {
@@ -187,156 +202,185 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         }
     }
     const int* table = kv.table + (long long)slot * kv.table_width;
-    auto load_ids = [&](int base) {
-        for (int j = tid; j < PT_IDS && base + j < n_pages; j += 128) {
-            int lp = first_page + base + j;
+    // Ids of the block's pages: a ring of PT_IDS entries in two halves.  Both halves are filled at the start;
+    // every 64 pages the rows refill the half whose pages are behind them with the pages 64 to 127 ahead.
+    auto load_ids = [&](int first, int count) {
+        for (int j = tid; j < count && first + j < n_pages; j += PT_ROWS) {
+            int lp = first_page + first + j;
             if (kv.ring_pages) lp %= kv.ring_pages;
-            s_pages[j] = max(table[lp], 0);
+            s_pages[(first + j) & (PT_IDS - 1)] = max(table[lp], 0);
         }
     };
-    load_ids(0);
+    if (owns_row) load_ids(0, PT_IDS);
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // Q was written by ordinary stores
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
-    const uint32_t tmem_row = tmem + ((uint32_t)(warp * 32) << 16);   // this warp's 32 lanes
+    const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes
     const uint32_t idesc_s = idesc(SB_PAGE, 0), idesc_o = idesc(PT_D, 1);
+    constexpr uint32_t O_COL = 2 * SB_PAGE;        // tensor memory: S buffers at columns 0 and 64, O from 128
 
-    auto issue_page = [&](int i) {   // thread 0: keys and values of the block's i-th page into stage i & 1
-        const int page = s_pages[i & (PT_IDS - 1)];
-        const int y = (page * kv.n_kv_heads + kvh) * SB_PAGE;
-        uint64_t* bar = &kv_full[i & 1];
-        mbar_expect_tx(bar, 2 * STAGE);
-        tma_load_2d(k_s + (i & 1) * STAGE, &map_k, 0, y, bar);
-        tma_load_2d(k_s + (i & 1) * STAGE + KV_ATOM, &map_k, 64, y, bar);
-        tma_load_2d(v_s + (i & 1) * STAGE, &map_v, 0, y, bar);
-        tma_load_2d(v_s + (i & 1) * STAGE + KV_ATOM, &map_v, 64, y, bar);
-    };
-
-    // The output accumulates in tensor memory across pages.  The probabilities of a page are taken
-    // relative to a reference maximum m_ref that is raised only when the row's maximum exceeds it by more
-    // than 8 (in the log2 domain): then the row's sum and its accumulator are rescaled once.  Until then
-    // a probability may be as large as 2^8, which bfloat16 and the 32-bit sums hold without loss, and
-    // the final division by the sum removes the common factor.
-    float m_ref = -INFINITY, l_run = 0.f;
-    const int lo_max = window > 0 ? max(0, pos_max - window + 1) : 0;
-
-    if (tid == 0) issue_page(0);
-    uint32_t kv_phase[2] = {0, 0}, s_phase = 0, o_phase = 0;
-    for (int i = 0; i < n_pages; ++i) {
-        if (((i + 1) & (PT_IDS - 1)) == 0) {   // the next page's id is in the next batch of ids
-            __syncthreads();
-            load_ids(i + 1);
-            __syncthreads();
-        }
-        const int stage = i & 1;
-        if (tid == 0) {
-            if (i + 1 < n_pages) issue_page(i + 1);   // its stage was last read by the products of page i - 1, which are done
-            mbar_wait(&kv_full[stage], kv_phase[stage], abort_flag, status);
-            tc_fence_after();
-            const unsigned char* kt = k_s + stage * STAGE;
+    if (!owns_row) {
+        // ---- the issuer: one thread.  Page i lives in stage i & 1; a barrier of index i & 1 is in phase (i >> 1) & 1
+        // when page i's event completes.
+        if (tid == PT_ROWS) {
+            auto issue_k = [&](int i) {
+                const int y = (s_pages[i & (PT_IDS - 1)] * kv.n_kv_heads + kvh) * SB_PAGE;
+                mbar_expect_tx(&k_full[i & 1], STAGE);
+                tma_load_2d(k_s + (i & 1) * STAGE, &map_k, 0, y, &k_full[i & 1]);
+                tma_load_2d(k_s + (i & 1) * STAGE + KV_ATOM, &map_k, 64, y, &k_full[i & 1]);
+            };
+            auto issue_v = [&](int i) {
+                const int y = (s_pages[i & (PT_IDS - 1)] * kv.n_kv_heads + kvh) * SB_PAGE;
+                mbar_expect_tx(&v_full[i & 1], STAGE);
+                tma_load_2d(v_s + (i & 1) * STAGE, &map_v, 0, y, &v_full[i & 1]);
+                tma_load_2d(v_s + (i & 1) * STAGE + KV_ATOM, &map_v, 64, y, &v_full[i & 1]);
+            };
+            auto issue_s = [&](int i) {   // S of page i into S buffer i & 1
+                mbar_wait(&k_full[i & 1], (i >> 1) & 1, abort_flag, status);
+                tc_fence_after();
+                const unsigned char* kt = k_s + (i & 1) * STAGE;
 #pragma unroll
-            for (int ks = 0; ks < PT_D / 16; ++ks)
-                tc_mma(tmem, desc_k_major(q_s + (ks >> 2) * Q_ATOM) + 2 * (ks & 3), desc_k_major(kt + (ks >> 2) * KV_ATOM) + 2 * (ks & 3),
-                       idesc_s, ks > 0 ? 1u : 0u);
-            tc_commit(s_done);
-        }
-        kv_phase[stage] ^= 1;
-        mbar_wait(s_done, s_phase, abort_flag, status);
-        s_phase ^= 1;
-        tc_fence_after();
-
-        // This thread's row of scores: mask (only where the page is not wholly visible), maximum, probabilities.
-        const int key0 = (first_page + i) * SB_PAGE;
-        float s[SB_PAGE];
-        tc_ld32(tmem_row, s);
-        tc_ld32(tmem_row + 32, s + 32);
-        const bool whole_page_visible = key0 + SB_PAGE - 1 <= pos_min && key0 >= lo_max && t_last == t0 + PT_ROWS - 1;
-        float mx = -INFINITY;
-        if (whole_page_visible) {
+                for (int ks = 0; ks < PT_D / 16; ++ks)
+                    tc_mma(tmem + (i & 1) * SB_PAGE, desc_k_major(q_s + (ks >> 2) * Q_ATOM) + 2 * (ks & 3),
+                           desc_k_major(kt + (ks >> 2) * KV_ATOM) + 2 * (ks & 3), idesc_s, ks > 0 ? 1u : 0u);
+                tc_commit(&s_done[i & 1]);
+            };
+            issue_k(0);
+            issue_v(0);
+            if (n_pages > 1) issue_k(1);
+            issue_s(0);
+            for (int i = 0; i < n_pages && !*abort_flag; ++i) {
+                const int b = i & 1;
+                // S of the next page: its buffer was read by the rows in iteration i - 1 (p_ready of i - 1, waited for below).
+                if (i + 1 < n_pages) issue_s(i + 1);
+                if (i + 2 < n_pages) {   // keys two pages ahead go into the stage of page i, once S has read it
+                    mbar_wait(&s_done[b], (i >> 1) & 1, abort_flag, status);
+                    issue_k(i + 2);
+                }
+                mbar_wait(p_ready, i & 1, abort_flag, status);        // P of page i is written (and O rescaled if need be)
+                mbar_wait(&v_full[b], (i >> 1) & 1, abort_flag, status);
+                if (*abort_flag) break;
+                tc_fence_after();
+                const unsigned char* vt = v_s + b * STAGE;
 #pragma unroll
-            for (int c = 0; c < SB_PAGE; ++c) mx = fmaxf(mx, s[c]);
-            mx *= scale_log2;   // scale_log2 > 0: the maximum commutes with it
-        } else {
-#pragma unroll
-            for (int c = 0; c < SB_PAGE; ++c) {
-                const int n = key0 + c;
-                if (!(n <= pos && n >= lo)) s[c] = -INFINITY;
-                mx = fmaxf(mx, s[c]);
+                for (int ks = 0; ks < SB_PAGE / 16; ++ks)   // 16 keys per step: 32 bytes along P's rows, two groups of eight key rows of V
+                    tc_mma(tmem + O_COL, desc_k_major(p_s) + 2 * ks, desc_mn_major(vt + ks * 2048, KV_ATOM), idesc_o,
+                           (i > 0 || ks > 0) ? 1u : 0u);
+                tc_commit(&o_done[b]);
+                if (i + 1 < n_pages) {   // values of the next page go into the stage of page i - 1, once its product is done
+                    if (i > 0) mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, status);
+                    issue_v(i + 1);
+                }
             }
-            mx *= scale_log2;
+            if (*abort_flag) {   // leaving early: give the copies in flight a bounded time to land
+                const long long t_abort = clock64();
+                while (clock64() - t_abort < (1ll << 22)) {}
+            }
         }
-        float alpha = 1.0f;
-        if (mx > m_ref + 8.0f || m_ref == -INFINITY) {
-            const float m_new = fmaxf(m_ref, mx);
-            alpha = m_new == -INFINITY ? 1.0f : exp2f(m_ref - m_new);   // 0 when the reference was -inf
-            m_ref = m_new;
+    } else {
+        // ---- the rows.  The output accumulates in tensor memory across pages.  The probabilities of a page are
+        // taken relative to a reference maximum m_ref that is raised only when the row's maximum exceeds it by
+        // more than 8 (in the log2 domain): then the row's sum and its accumulator are rescaled once.  Until then
+        // a probability may be as large as 2^8, which bfloat16 and the 32-bit sums hold without loss, and
+        // the final division by the sum removes the common factor.
+        float m_ref = -INFINITY, l_run = 0.f;
+        const int lo_max = window > 0 ? max(0, pos_max - window + 1) : 0;
+        for (int i = 0; i < n_pages; ++i) {
+            const int b = i & 1;
+            if (i > 0 && (i & 63) == 0) load_ids(i + 64, 64);   // read by the issuer 62 pages (and as many barriers) from now
+            mbar_wait(&s_done[b], (i >> 1) & 1, abort_flag, status);
+            if (*abort_flag) break;
+            tc_fence_after();
+
+            // This thread's row of scores: mask (only where the page is not wholly visible), maximum, probabilities.
+            const int key0 = (first_page + i) * SB_PAGE;
+            float s[SB_PAGE];
+            tc_ld32(tmem_row + b * SB_PAGE, s);
+            tc_ld32(tmem_row + b * SB_PAGE + 32, s + 32);
+            tc_fence_before();   // ordered before the arrival below, after which the issuer may overwrite this buffer
+            const bool whole_page_visible = key0 + SB_PAGE - 1 <= pos_min && key0 >= lo_max && t_last == t0 + PT_ROWS - 1;
+            if (!whole_page_visible) {
+#pragma unroll
+                for (int c = 0; c < SB_PAGE; ++c) {
+                    const int n = key0 + c;
+                    if (!(n <= pos && n >= lo)) s[c] = -INFINITY;
+                }
+            }
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one of 64 steps
+#pragma unroll
+            for (int c = 0; c < SB_PAGE; c += 4) {
+                mx4[0] = fmaxf(mx4[0], s[c]); mx4[1] = fmaxf(mx4[1], s[c + 1]);
+                mx4[2] = fmaxf(mx4[2], s[c + 2]); mx4[3] = fmaxf(mx4[3], s[c + 3]);
+            }
+            const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale_log2 > 0: the maximum commutes with it
+            float alpha = 1.0f;
+            if (mx > m_ref + 8.0f || m_ref == -INFINITY) {
+                const float m_new = fmaxf(m_ref, mx);
+                alpha = m_new == -INFINITY ? 1.0f : exp2f(m_ref - m_new);   // 0 when the reference was -inf
+                m_ref = m_new;
+            }
+            const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
+            uint4 packed[SB_PAGE / 8];
+            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+            for (int c = 0; c < SB_PAGE; c += 8) {
+                __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed[c >> 3]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const float p0 = fast_exp2(fmaf(s[c + 2 * e], scale_log2, -m_use)), p1 = fast_exp2(fmaf(s[c + 2 * e + 1], scale_log2, -m_use));
+                    sum4[e] += p0 + p1;
+                    h2[e] = __floats2bfloat162_rn(p0, p1);
+                }
+            }
+            l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+
+            // O += P V of the page before must be done before P is overwritten or the accumulator rescaled.  It was
+            // issued before this iteration began, so this wait is over by the time the arithmetic above is.
+            if (i > 0) {
+                mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, status);
+                if (*abort_flag) break;
+                tc_fence_after();
+            }
+            // the accumulator of earlier pages moves to the new reference (rare after the first pages)
+            if (i > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+#pragma unroll
+                for (int d0 = 0; d0 < PT_D; d0 += 32) {
+                    float o[32];
+                    tc_ld32(tmem_row + O_COL + d0, o);
+#pragma unroll
+                    for (int d = 0; d < 32; ++d) o[d] *= alpha;
+                    tc_st32(tmem_row + O_COL + d0, o);
+                }
+            }
+#pragma unroll
+            for (int c = 0; c < SB_PAGE / 8; ++c)
+                *reinterpret_cast<uint4*>(p_s + tid * 128 + (((c ^ (tid & 7))) << 4)) = packed[c];
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P was written by ordinary stores
+            tc_fence_before();
+            mbar_arrive(p_ready);
         }
-        const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
-        // the accumulator of earlier pages moves to the new reference (rare after the first pages)
-        if (i > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
+        if (!*abort_flag) {   // the last product, then this row's output
+            mbar_wait(&o_done[(n_pages - 1) & 1], ((n_pages - 1) >> 1) & 1, abort_flag, status);
+            tc_fence_after();
+        }
+        if (!*abort_flag) {
+            const float inv = 1.0f / l_run;
+            __nv_bfloat16* o_row = out + ((long long)(row0 + (t < total ? t / G : 0)) * n_heads + kvh * G + (t < total ? t % G : 0)) * PT_D;
 #pragma unroll
             for (int d0 = 0; d0 < PT_D; d0 += 32) {
                 float o[32];
-                tc_ld32(tmem_row + SB_PAGE + d0, o);
+                tc_ld32(tmem_row + O_COL + d0, o);
+                if (t < total) {
 #pragma unroll
-                for (int d = 0; d < 32; ++d) o[d] *= alpha;
-                tc_st32(tmem_row + SB_PAGE + d0, o);
-            }
-        }
-        float sum = 0.f;
+                    for (int d = 0; d < 32; d += 8) {
+                        uint4 packed;
+                        __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
 #pragma unroll
-        for (int c = 0; c < SB_PAGE; c += 8) {
-            uint4 packed;
-            __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float p0 = exp2f(fmaf(s[c + 2 * e], scale_log2, -m_use)), p1 = exp2f(fmaf(s[c + 2 * e + 1], scale_log2, -m_use));
-                sum += p0 + p1;
-                h2[e] = __floats2bfloat162_rn(p0, p1);
-            }
-            *reinterpret_cast<uint4*>(p_s + tid * 128 + ((((c >> 3) ^ (tid & 7))) << 4)) = packed;
-        }
-        l_run = l_run * alpha + sum;
-        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P was written by ordinary stores
-        tc_fence_before();
-        __syncthreads();
-        if (*abort_flag) break;
-        if (tid == 0) {
-            tc_fence_after();
-            const unsigned char* vt = v_s + stage * STAGE;
-#pragma unroll
-            for (int ks = 0; ks < SB_PAGE / 16; ++ks)   // 16 keys per step: 32 bytes along P's rows, two groups of eight key rows of V
-                tc_mma(tmem + SB_PAGE, desc_k_major(p_s) + 2 * ks, desc_mn_major(vt + ks * 2048, KV_ATOM), idesc_o,
-                       (i > 0 || ks > 0) ? 1u : 0u);
-            tc_commit(o_done);
-        }
-        // The product must be done before the next page rescales the accumulator, overwrites P or reuses the stage.
-        mbar_wait(o_done, o_phase, abort_flag, status);
-        o_phase ^= 1;
-        tc_fence_after();
-        // (a time-out here is acted on after the next block-wide barrier, where all threads see it together)
-    }
-    if (*abort_flag && tid == 0) {   // leaving early: give the copy in flight a bounded time to land
-        const long long t_abort = clock64();
-        while (clock64() - t_abort < (1ll << 22)) {}
-    }
-    if (!*abort_flag) {
-        const float inv = 1.0f / l_run;
-        __nv_bfloat16* o_row = out + ((long long)(row0 + (t < total ? t / G : 0)) * n_heads + kvh * G + (t < total ? t % G : 0)) * PT_D;
-#pragma unroll
-        for (int d0 = 0; d0 < PT_D; d0 += 32) {
-            float o[32];
-            tc_ld32(tmem_row + SB_PAGE + d0, o);
-            if (t < total) {
-#pragma unroll
-                for (int d = 0; d < 32; d += 8) {
-                    uint4 packed;
-                    __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed);
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
-                    *reinterpret_cast<uint4*>(o_row + d0 + d) = packed;
+                        for (int e = 0; e < 4; ++e) h2[e] = __floats2bfloat162_rn(o[d + 2 * e] * inv, o[d + 2 * e + 1] * inv);
+                        *reinterpret_cast<uint4*>(o_row + d0 + d) = packed;
+                    }
                 }
             }
         }
@@ -386,7 +430,7 @@ extern "C" int sb_attn_prefill_tc(const void* q, void* out, SbBatch batch, SbKV 
                                   int max_q_len, int n_pages, int* status, cudaStream_t stream) {
     if (batch.n_rows <= 0) return 0;
     if (kv.head_dim != PT_D || n_heads % kv.n_kv_heads || max_q_len < 1 || n_pages < 1) return (int)cudaErrorInvalidValue;
-    const int smem = 2 * PT_ROWS * 128 + 4 * 2 * SB_PAGE * 128 + PT_ROWS * 128 + 64 + PT_IDS * 4;
+    const int smem = 2 * PT_ROWS * 128 + 4 * 2 * SB_PAGE * 128 + PT_ROWS * 128 + 96 + PT_IDS * 4;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -403,7 +447,7 @@ extern "C" int sb_attn_prefill_tc(const void* q, void* out, SbBatch batch, SbKV 
     const long long tiles = ((long long)max_q_len * G + PT_ROWS - 1) / PT_ROWS;
     if (tiles > 2147483647LL || kv.n_kv_heads > 65535 || batch.n_seqs > 65535) return (int)cudaErrorInvalidValue;
     dim3 grid((unsigned int)tiles, kv.n_kv_heads, batch.n_seqs);
-    sb_launch(attn_prefill_tc_kernel, grid, 128, smem, stream, mk, mv, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv, n_heads,
+    sb_launch(attn_prefill_tc_kernel, grid, PT_THREADS, smem, stream, mk, mv, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv, n_heads,
               scale * 1.4426950408889634f, window, status);
     return (int)cudaGetLastError();
 }

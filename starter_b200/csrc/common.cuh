@@ -49,6 +49,14 @@ template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float
 // The value as it reads back after being stored in T.
 template <class T> __device__ __forceinline__ float rnd(float v) { return to_f<T>(from_f<T>(v)); }
 
+// 2^x in one instruction (relative error 2^-22, tiny results flushed to zero; 2^-inf = 0).  The probabilities of
+// the attention kernels are rounded to bfloat16 right after, so the full-precision routine buys nothing there.
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -4,6 +4,7 @@ kernels the same way (engine/kernels/gemm.py:477-513).
 
     python -m starter_b200.csrc.microbench --kernel stream --shape gateup --rows 8
     python -m starter_b200.csrc.microbench --kernel attn_decode --rows 8 --context 4096
+    python -m starter_b200.csrc.microbench --kernel attn_prefill --tokens 2048 --context 2048
 """
 
 from __future__ import annotations
@@ -90,20 +91,48 @@ def bench_attn_decode(ops, rows: int, context: int, heads: int, kv_heads: int, h
             "GB/s": round(nbytes / us / 1e3, 1)}
 
 
+def bench_attn_prefill(ops, tokens: int, context: int, heads: int, kv_heads: int, head_dim: int, layers: int):
+    """One sequence that holds ``context - tokens`` tokens and brings ``tokens`` new ones."""
+    from ..cache import Cache, KVRequest
+    from ..engine.context import Runtime, StepContext
+    dtype = torch.bfloat16
+    cache = Cache([KVRequest(kv_heads, head_dim)] * layers, n_slots=1, max_tokens=context, dtype=dtype, device="cuda",
+                  max_seq_tokens=context, max_step_tokens=tokens)
+    cache.groups[0].k.normal_()
+    cache.groups[0].v.normal_()
+    slot = cache.alloc()
+    cache.reserve(slot, context)
+    cache.assume_length(slot, context - tokens)
+    cache.flush()
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+    ctx = StepContext(runtime=Runtime(dtype, torch.device("cuda"), ops), cache=cache, n_seqs=1, n_rows=tokens, max_q_len=tokens,
+                      kv_bound=context, seq_slot=i32([slot]), cu_q=i32([0, tokens]), row_seq=i32([0] * tokens),
+                      lengths=cache.lengths, status=torch.zeros(1, dtype=torch.int32, device="cuda"))
+    q = torch.randn(tokens, heads * head_dim, device="cuda", dtype=dtype)
+    calls = [lambda lc=lc: ops.attention(ctx, q, lc, heads, 1.0 / math.sqrt(head_dim), None) for lc in cache.layers]
+    us = time_graph(calls)
+    start = context - tokens
+    flops = 4.0 * head_dim * heads * (tokens * start + tokens * (tokens + 1) / 2.0)
+    return {"kernel": "attn_prefill", "tokens": tokens, "context": context, "us": round(us, 2), "TFLOP/s": round(flops / us / 1e6, 1)}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--kernel", required=True, choices=["stream", "skinny", "cublas", "attn_decode"])
+    ap.add_argument("--kernel", required=True, choices=["stream", "skinny", "cublas", "attn_decode", "attn_prefill"])
     ap.add_argument("--shape", default="gateup", choices=sorted(SHAPES))
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--copies", type=int, default=12, help="copies of the weights the graph walks through")
     ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--tokens", type=int, default=2048, help="attn_prefill: new tokens of the sequence")
     ap.add_argument("--layers", type=int, default=8, help="attn_decode: layers of cache the graph walks through")
     ap.add_argument("--dependent-launch", action="store_true", help="launch with programmatic dependent launch")
     args = ap.parse_args(argv)
     from .ops import get_ops
     ops = get_ops(verbose=False)
     ops.set_dependent_launch(args.dependent_launch)
-    if args.kernel == "attn_decode":
+    if args.kernel == "attn_prefill":
+        out = bench_attn_prefill(ops, args.tokens, max(args.context, args.tokens), 32, 8, 128, args.layers)
+    elif args.kernel == "attn_decode":
         out = bench_attn_decode(ops, args.rows, args.context, 32, 8, 128, args.layers)
     else:
         out = bench_product(ops, args.kernel, args.shape, args.rows, args.copies)

@@ -340,6 +340,37 @@ def test_prefill_attention_over_many_pages(ops, ref, heads, kv_heads, head_dim, 
         assert float((got - want).abs().max()) < 0.05 * float(want.abs().max())
 
 
+def test_prefill_attention_far_into_a_long_context(ops, ref):
+    """A piece appended after 9,000 cached tokens: more pages than the kernel keeps ids for at a time (its
+    ring of page ids is refilled on the way), and products that run a page ahead of the softmax throughout."""
+    dtype, heads, kv_heads, head_dim = torch.bfloat16, 8, 2, 128
+    cache = Cache([KVRequest(kv_heads, head_dim, None)], n_slots=2, max_tokens=64 * 150, dtype=dtype, device="cuda",
+                  max_step_tokens=512)
+    g = cache.groups[0]
+    g.k.copy_(rand(tuple(g.k.shape), dtype, 90))
+    g.v.copy_(rand(tuple(g.v.shape), dtype, 91))
+    slot = cache.alloc()
+    cache.reserve(slot, 9000 + 300)
+    cache.assume_length(slot, 9000)
+    cache.flush()
+    ctx = make_ctx(cache, ops, [slot], [300], dtype)
+    qkv = rand((300, (heads + 2 * kv_heads) * head_dim), dtype, 92, 0.5)
+    page = int(g.table_host[slot, 8500 // 64])
+    g.k[0, page, 0, 8500 % 64] = 3.0          # key 8,500 is large and the last query of head 0 points at it
+    qkv[-1, :head_dim] = 3.0
+    outs = []
+    k0, v0 = g.k.clone(), g.v.clone()
+    for o in (ops, ref):
+        q = o.qk_norm_rope_store(ctx, qkv, cache.layers[0], heads, kv_heads, head_dim, None, None, 0.0, None)
+        outs.append(o.attention(ctx, q, cache.layers[0], heads, 1.0 / math.sqrt(head_dim), None))
+        g.k.copy_(k0)
+        g.v.copy_(v0)
+    close(outs[0], outs[1], dtype, "prefill attention, long context")
+    want = g.v[0, page, 0, 8500 % 64].float()
+    assert float((outs[0][-1, :head_dim].float() - want).abs().max()) < 0.05 * float(want.abs().max())
+    assert ops.read_kernel_status() == 0
+
+
 @pytest.mark.parametrize("shape", [(1, 6144, 2560), (8, 2560, 9728), (16, 1000, 4104), (33, 2560, 4096), (20, 700, 520),
                                    (64, 151936, 256), (5, 130, 72)])
 def test_stream_product(ops, ref, shape):
