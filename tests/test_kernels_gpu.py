@@ -190,7 +190,7 @@ def test_sampling_matches_plain(ops, top_k):
             assert got[r] == tok, f"row {r}: {got[r]} != {tok} (margin {margin:.2g})"
 
 
-@pytest.mark.parametrize("splits", [None, 1, 3])
+@pytest.mark.parametrize("splits", [None, 1, 3, 5, 6, 7, 12])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(8, 2, 128, None), (16, 1, 64, None), (6, 3, 64, 100), (4, 4, 128, 700)])
 def test_decode_attention(ops, ref, monkeypatch, heads, kv_heads, head_dim, window, splits):
     """One new token per sequence over contexts of 0 to 1500 tokens, against the torch restatement;
@@ -286,7 +286,7 @@ def test_decode_attention_with_preparation_inside(ops, ref, monkeypatch, heads, 
 
 @pytest.mark.parametrize("M", [1, 5, 8, 11, 16])
 @pytest.mark.parametrize("splits,tiled,warps", [(1, False, 8), (3, False, 8), (2, True, 8), (1, True, 4), (2, False, 4), (8, False, 4),
-                                                (11, False, 8), (3, True, 8), (11, True, 4)])
+                                                (11, False, 8), (3, True, 8), (11, True, 4), (5, True, 8), (6, False, 4), (7, True, 4)])
 def test_skinny_product_variants(ops, ref, M, splits, tiled, warps):
     """The weight-streaming product with every row tile, K slicing, way of meeting (cluster, scratch) and weight
     layout (row-major, tile-major copy), with and without the SwiGLU epilogue, at sizes that are no multiples
