@@ -67,12 +67,15 @@ __global__ void rmsnorm_vec_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfl
                                    const W* __restrict__ weight, __nv_bfloat16* __restrict__ out, int width, float eps) {
     __shared__ float red[33];
     sb_stamp(1, 0);
-    pdl_wait();
-    pdl_launch_dependents();
-    sb_stamp(1, 1);
     const long long base = (long long)blockIdx.x * width;
     const int c = threadIdx.x * 8;
     const bool active = c < width;
+    float wv[8];   // the norm's weights do not depend on the kernel before this one: asked for before the wait
+#pragma unroll
+    for (int e = 0; e < 8; ++e) wv[e] = active ? to_f<W>(weight[c + e]) : 0.f;
+    pdl_wait();
+    pdl_launch_dependents();
+    sb_stamp(1, 1);
     float v[8];
 #pragma unroll
     for (int e = 0; e < 8; ++e) v[e] = 0.f;
@@ -112,7 +115,7 @@ __global__ void rmsnorm_vec_kernel(__nv_bfloat16* __restrict__ x, const __nv_bfl
 #pragma unroll
         for (int e = 0; e < 4; ++e) {
             const float n0 = rnd<__nv_bfloat16>(__fmul_rn(v[2 * e], rstd)), n1 = rnd<__nv_bfloat16>(__fmul_rn(v[2 * e + 1], rstd));
-            rh[e] = __floats2bfloat162_rn(__fmul_rn(n0, to_f<W>(weight[c + 2 * e])), __fmul_rn(n1, to_f<W>(weight[c + 2 * e + 1])));
+            rh[e] = __floats2bfloat162_rn(__fmul_rn(n0, wv[2 * e]), __fmul_rn(n1, wv[2 * e + 1]));
         }
         *reinterpret_cast<uint4*>(out + base + c) = res;
     }
