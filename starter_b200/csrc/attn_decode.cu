@@ -52,6 +52,8 @@ struct SbFusedQK {
     int norm_f32;
     int store_kv;
     int reserved;
+    const void* next_w;        // a matrix (16-byte aligned) that the kernel after this one streams: asked into L2 when
+    long long next_bytes;      // this kernel's keys are read, so that memory stays busy through its merge; or null
 };
 
 __device__ __forceinline__ void unpack4(const uint2 raw, float (&v)[4]) {
@@ -294,6 +296,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restric
         __syncwarp();
     }
     cp_async_wait<0>();
+    if (FUSED && tid == 0)
+        l2_prefetch_share(fused.next_w, fused.next_bytes, ((long long)blockIdx.z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x,
+                          (long long)gridDim.x * gridDim.y * gridDim.z);
     sb_stamp(4, 3);
 #pragma unroll
     for (int h = 0; h < 2; ++h) {

@@ -114,6 +114,22 @@ __device__ __forceinline__ long long kv_offset(const SbKV& kv, int slot, int pos
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Ask for `bytes` at p to be brought into L2 without waiting for them (p 16-byte aligned, bytes a multiple of 16).
+__device__ __forceinline__ void l2_prefetch(const void* p, unsigned int bytes) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(bytes) : "memory");
+}
+
+// Share `part` of `parts` of the range [p, p + total): one thread asks for it in pieces of 16 KB.
+__device__ __forceinline__ void l2_prefetch_share(const void* p, long long total, long long part, long long parts) {
+    if (p == nullptr || total <= 0) return;
+    const long long share = (((total + parts - 1) / parts) + 255) & ~255ll;
+    long long lo = part * share;
+    const long long hi = lo + share < total ? lo + share : (total & ~15ll);
+    constexpr long long PIECE = 16384;
+    for (; lo < hi; lo += PIECE)
+        l2_prefetch(reinterpret_cast<const unsigned char*>(p) + lo, (unsigned int)(hi - lo < PIECE ? hi - lo : PIECE));
+}
+
 // Tuning aid, compiled in with -DSB_TIMELINE only: thread 0 of a block appends (time, kernel, milestone, block)
 // to a log on the device, from which a script draws the step's timeline.  Each source file has its own
 // pointer to the log, set through the function that SB_TIMELINE_SETTER defines for it.

@@ -38,7 +38,8 @@ class SbKV(Structure):
 
 class SbFusedQK(Structure):
     _fields_ = [("qkv", c_void_p), ("q_norm", c_void_p), ("k_norm", c_void_p), ("cos_t", c_void_p), ("sin_t", c_void_p),
-                ("status", c_void_p), ("eps", c_float), ("norm_f32", c_int), ("store_kv", c_int), ("reserved", c_int)]
+                ("status", c_void_p), ("eps", c_float), ("norm_f32", c_int), ("store_kv", c_int), ("reserved", c_int),
+                ("next_w", c_void_p), ("next_bytes", c_longlong)]
 
 
 def _code(dtype: torch.dtype) -> int:
@@ -108,6 +109,7 @@ class Ops:
         self._kernel_status = None
         self.decode_balanced = os.environ.get("STARTER_B200_ATTN", "balanced") != "split"
         self.fuse_qk = os.environ.get("STARTER_B200_FUSE_QK", "1") != "0"
+        self.prefetch_next_bytes = int(os.environ.get("STARTER_B200_PREFETCH_MAX", 24 << 20))
         self.prefill_tensor_memory = os.environ.get("STARTER_B200_PREFILL", "tc") != "mma"
 
     # ---- plumbing -----------------------------------------------------------------------
@@ -402,7 +404,8 @@ class Ops:
         pairs = ctx.n_seqs * kv.n_kv_heads
         return not (self.decode_balanced and pairs > self.decode_resident(kv.head_dim) and ctx.n_seqs <= 1024)
 
-    def qk_attention(self, ctx, qkv, layer_cache, n_heads, n_kv_heads, head_dim, q_norm, k_norm, eps, rotary, scale, window):
+    def qk_attention(self, ctx, qkv, layer_cache, n_heads, n_kv_heads, head_dim, q_norm, k_norm, eps, rotary, scale, window,
+                     then=None):
         """qk_norm_rope_store and attention in one kernel, for the steps that the split-key decode kernel serves and a
         rotary encoding over the whole head (or none).  Returns None when the step is not of that kind: the caller then
         makes the two calls."""
@@ -430,8 +433,14 @@ class Ops:
                 norm_f32 = int(w.dtype == torch.float32)
         if q_norm is not None and k_norm is not None and q_norm.dtype != k_norm.dtype:
             return None
+        # `then`: the matrix that the next product streams; the kernel asks for it into L2 as it finishes its keys
+        next_w, next_bytes = None, 0
+        if then is not None and self.prefetch_next_bytes > 0 and then.dtype == torch.bfloat16:
+            copy = getattr(then, "_sb_tiled", None)
+            src = copy[0] if copy is not None and ctx.n_rows <= self.SKINNY_MAX_ROWS else then
+            next_w, next_bytes = c_void_p(src.data_ptr()), min(src.numel() * 2, self.prefetch_next_bytes) & ~15
         fused = SbFusedQK(_ptr(qkv), _ptr(q_norm), _ptr(k_norm), _ptr(cos), _ptr(sin), _ptr(ctx.status), float(eps), norm_f32,
-                          int(n_kv_heads > 0), 0)
+                          int(n_kv_heads > 0), 0, next_w, next_bytes)
         out = torch.empty((qkv.shape[0], n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
         n_splits = self.decode_splits(ctx.n_seqs, kv.n_kv_heads, layer_cache.group.table_width, kv.head_dim)
         partial, counters = self._decode_scratch(qkv.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, n_splits)

@@ -75,7 +75,7 @@ class Attention:
         one_call = getattr(self.ops, "qk_attention", None)   # optional: both steps in one kernel where the ops have it
         if one_call is not None:
             a = one_call(ctx, qkv, layer_cache, self.num_heads, n_kv, self.head_dim, self.q_norm, self.k_norm,
-                         self.norm_eps, rotary, self.scale, self.window)
+                         self.norm_eps, rotary, self.scale, self.window, then=self.w_o)
         if a is None:
             q = self.ops.qk_norm_rope_store(ctx, qkv, layer_cache, self.num_heads, n_kv, self.head_dim,
                                             self.q_norm, self.k_norm, self.norm_eps, rotary)
