@@ -14,7 +14,8 @@
 // Limits and rules:
 //  * The array holds SB_NOALLOC_MAX_COUNTERS counters and SB_NOALLOC_MAX_FLOATS floats of partial
 //    results (16 MiB + 16 KiB).  Every GPU that loads the library holds that much until the
-//    process exits.  A call needs n_seqs * n_kv_heads counters and, when n_splits > 1,
+//    process exits.  A call needs n_seqs * n_kv_heads counters and, when n_splits > 8 (up to 8 splits
+//    merge through shared memory and use no scratch),
 //    n_seqs * n_heads * n_splits * (head_dim + 2) floats; a call that needs more is refused
 //    with SB_NOALLOC_TOO_LARGE and sb_attn_decode_noalloc_error() says what was asked for.
 //  * The first call on a device looks the array's device address up (cudaGetSymbolAddress)

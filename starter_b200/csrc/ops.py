@@ -269,8 +269,9 @@ class Ops:
 
     def skinny_splits(self, blocks: int, K: int) -> int:
         """K slices per block of 16 weight rows: enough blocks for three per SM, but no slice
-        shorter than 3072 columns (measured on the 4B shapes: short slices cost more in the
-        pass through scratch memory than they gain in parallelism)."""
+        shorter than 3072 columns (measured on the 4B shapes, in the decode step, with the slices
+        meeting through cluster shared memory: short slices cost more in the meeting than they
+        gain in parallelism; 1 slice for q/k/v, output and gate/up, 3 for down)."""
         return max(1, min(round(3 * self.sm_count() / blocks), K // 3072))
 
     def skinny_warps(self, n_blocks: int) -> int:
