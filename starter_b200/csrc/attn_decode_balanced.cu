@@ -129,6 +129,20 @@ attn_decode_balanced_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
             __syncwarp();
             const unsigned char* ks = my_pipe + (i % AD_STAGES) * 2 * SLICE;
             const unsigned char* vs = ks + SLICE;
+            // Values of keys that no row of this step may see (beyond the new token, before the window) are stale: they
+            // meet a probability of exactly zero, but zero times an infinity or a NaN left by the page's former owner
+            // would not be zero.  Such rows exist only in a sequence's last (and, with a window, first) page.
+            {
+                const int n_base = (p_begin + i) * SB_PAGE + warp * AD_KEYS_PER_WARP;
+                if (n_base + AD_KEYS_PER_WARP - 1 > pos || n_base < lo) {
+                    for (int j = lane; j < AD_KEYS_PER_WARP * CH; j += 32) {
+                        const int r = j / CH, n = n_base + r;
+                        if (n > pos || n < lo)
+                            *reinterpret_cast<uint4*>(const_cast<unsigned char*>(vs) + tile_off<D>(r, j % CH)) = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    __syncwarp();
+                }
+            }
 
             float s0[4] = {0.f, 0.f, 0.f, 0.f}, s1[4] = {0.f, 0.f, 0.f, 0.f};
     #pragma unroll

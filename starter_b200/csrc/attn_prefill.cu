@@ -118,6 +118,17 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
         const unsigned char* ks = kv_s + (i & 1) * 2 * TILE;
         const unsigned char* vs = ks + TILE;
         const int key0 = (first_page + i) * SB_PAGE;
+        // Values of keys that no row of this block may see (beyond its last position, before its first window)
+        // are stale: they meet probabilities of exactly zero, but zero times an infinity or a NaN left by the
+        // page's former owner would not be zero.  Only a block's last (and, with a window, first) page has such rows.
+        if (key0 + SB_PAGE - 1 > pos_max || key0 < lo_min) {
+            for (int j = tid; j < SB_PAGE * CH; j += AP_WARPS * 32) {
+                const int r = j / CH, n = key0 + r;
+                if (n > pos_max || n < lo_min)
+                    *reinterpret_cast<uint4*>(const_cast<unsigned char*>(vs) + tile_off<D>(r, j % CH)) = make_uint4(0u, 0u, 0u, 0u);
+            }
+            __syncthreads();
+        }
         // A warp whose rows all lie before this page, or whose windows all lie after it, has nothing here.
         const int w_first = t0 + warp * 16, w_last = min(w_first + 15, total - 1);
         const bool warp_has = w_first < total && key0 <= start + w_last / G &&

@@ -354,6 +354,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     tc_st32(tmem_row + O_COL + d0, o);
                 }
             }
+            // Values of keys that no row of this block may see (beyond its last position, before its first window)
+            // are stale: they meet probabilities of exactly zero, but zero times an infinity or a NaN left by the
+            // page's former owner would not be zero.  Only a block's last (and, with a window, first) page has such
+            // rows; thread k clears the row of key k once the values have landed.
+            if (key0 + SB_PAGE - 1 > pos_max || key0 < lo_min) {
+                mbar_wait(&v_full[b], (i >> 1) & 1, abort_flag, status);
+                if (*abort_flag) break;
+                if (tid < SB_PAGE && (key0 + tid > pos_max || key0 + tid < lo_min)) {
+                    unsigned char* vt = v_s + b * STAGE;
+#pragma unroll
+                    for (int c = 0; c < 16; ++c)   // [2 blocks of 64 columns][64 keys][128 bytes]: the whole row, whatever the swizzle
+                        *reinterpret_cast<uint4*>(vt + (c >> 3) * KV_ATOM + tid * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                }
+            }
 #pragma unroll
             for (int c = 0; c < SB_PAGE / 8; ++c)
                 *reinterpret_cast<uint4*>(p_s + tid * 128 + (((c ^ (tid & 7))) << 4)) = packed[c];

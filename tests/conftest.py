@@ -20,7 +20,9 @@ from starter_b200.config import config_from_dict  # noqa: E402
 from starter_b200.weights import write_model_folder  # noqa: E402
 
 # Tiny A and B are the two small configurations the benchmark description names; W adds
-# sliding-window layers.  They differ in every size and option.
+# sliding-window layers.  They differ in every size and option.  M and N have the head sizes (128, 64)
+# that the tensor-core attention kernels take, so that the engine as a whole runs on those kernels too
+# (fused decode attention, tcgen05 and mma.sync prefill attention, with and without a window).
 TINY = {
     "A": dict(hidden_size=64, intermediate_size=160, num_hidden_layers=2, num_attention_heads=4,
               num_key_value_heads=2, head_dim=16, vocab_size=256, rms_norm_eps=1e-6, rope_theta=10000.0,
@@ -32,6 +34,13 @@ TINY = {
               num_key_value_heads=5, head_dim=48, vocab_size=301, rms_norm_eps=3e-6, rope_theta=500000.0,
               tie_word_embeddings=False, use_sliding_window=True, sliding_window=40,
               layer_types=["full_attention", "sliding_attention", "full_attention", "sliding_attention"], seed=2),
+    "M": dict(hidden_size=512, intermediate_size=1408, num_hidden_layers=3, num_attention_heads=8,
+              num_key_value_heads=2, head_dim=128, vocab_size=5003, rms_norm_eps=1e-6, rope_theta=1000000.0,
+              tie_word_embeddings=True, use_sliding_window=True, sliding_window=70,
+              layer_types=["full_attention", "sliding_attention", "full_attention"], seed=3),
+    "N": dict(hidden_size=384, intermediate_size=1000, num_hidden_layers=2, num_attention_heads=6,
+              num_key_value_heads=3, head_dim=64, vocab_size=3001, rms_norm_eps=1e-5, rope_theta=10000.0,
+              tie_word_embeddings=False, seed=4),
 }
 
 

@@ -190,6 +190,21 @@ def test_sampling_matches_plain(ops, top_k):
             assert got[r] == tok, f"row {r}: {got[r]} != {tok} (margin {margin:.2g})"
 
 
+def poison_beyond(cache, slots, lengths_after):
+    """NaN in every cache position of a sequence's last page that lies beyond the tokens it will hold after the
+    step: what a page's former owner may have left there must not reach any result."""
+    g = cache.groups[0]
+    for s, n in zip(slots, lengths_after):
+        if n % 64 == 0:
+            continue
+        lp = (n - 1) // 64
+        if g.ring_pages:
+            lp %= g.ring_pages
+        page = int(g.table_host[s, lp])
+        g.k[:, page, :, n % 64:] = float("nan")
+        g.v[:, page, :, n % 64:] = float("nan")
+
+
 @pytest.mark.parametrize("splits", [None, 1, 3, 5, 6, 7, 12])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(8, 2, 128, None), (16, 1, 64, None), (6, 3, 64, 100), (4, 4, 128, 700)])
 def test_decode_attention(ops, ref, monkeypatch, heads, kv_heads, head_dim, window, splits):
@@ -212,6 +227,7 @@ def test_decode_attention(ops, ref, monkeypatch, heads, kv_heads, head_dim, wind
         cache.assume_length(s, n)
         cache.reserve(s, n + 1)
     cache.flush()
+    poison_beyond(cache, slots, [n + 1 for n in lengths])
     ctx = make_ctx(cache, ops, slots, [1] * len(lengths), dtype)
     qkv = rand((len(lengths), (heads + 2 * kv_heads) * head_dim), dtype, 62)
     if window is None:  # key 37 of the last sequence is large and the new query of head 0 points at it
@@ -256,6 +272,7 @@ def test_decode_attention_with_preparation_inside(ops, ref, monkeypatch, heads, 
         cache.assume_length(s, n)
         cache.reserve(s, n + 1)
     cache.flush()
+    poison_beyond(cache, slots, [n + 1 for n in lengths])
     ctx = make_ctx(cache, ops, slots, [1] * len(lengths), dtype)
     n_kv = kv_heads if store else 0
     qkv = rand((len(lengths), (heads + 2 * n_kv) * head_dim), dtype, 82)
@@ -277,11 +294,12 @@ def test_decode_attention_with_preparation_inside(ops, ref, monkeypatch, heads, 
     q = ref.qk_norm_rope_store(ctx, qkv, cache.layers[0], heads, n_kv, head_dim, q_w, k_w, 1e-5, tables)
     want = ref.attention(ctx, q, cache.layers[0], heads, scale, window)
     close(got, want, dtype, "decode attention with q/k preparation inside")
-    close(k_got, g.k, dtype, "keys left in the cache")
-    assert torch.equal(v_got, g.v)
+    assert torch.equal(k_got.isnan(), g.k.isnan())          # the poison beyond the sequences stays where it was
+    close(k_got.nan_to_num(), g.k.nan_to_num(), dtype, "keys left in the cache")
+    assert torch.equal(v_got.nan_to_num(), g.v.nan_to_num())
     assert int(ctx.status.item()) == 0
     if not store:
-        assert torch.equal(k_got, k0)
+        assert torch.equal(k_got.nan_to_num(), k0.nan_to_num())
 
 
 @pytest.mark.parametrize("M", [1, 5, 8, 11, 16])
@@ -353,6 +371,7 @@ def test_prefill_attention_far_into_a_long_context(ops, ref):
     cache.reserve(slot, 9000 + 300)
     cache.assume_length(slot, 9000)
     cache.flush()
+    poison_beyond(cache, [slot], [9300])
     ctx = make_ctx(cache, ops, [slot], [300], dtype)
     qkv = rand((300, (heads + 2 * kv_heads) * head_dim), dtype, 92, 0.5)
     page = int(g.table_host[slot, 8500 // 64])
