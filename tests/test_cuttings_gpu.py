@@ -50,3 +50,33 @@ def test_dependent_launch_changes_no_bit(tiny_folders, dtype):
     for a, b in zip(got[False], got[True]):
         assert torch.equal(a, b)
     assert_close(got[True][:3], plain_logits(folder, seqs, dtype), dtype, "dependent launch")
+
+
+@pytest.mark.parametrize("route", ["stream", "balanced", "slices"])
+def test_other_kernel_routes_through_the_whole_engine(tiny_folders, monkeypatch, route):
+    """The shape rules send the test configurations to a few of the kernels only.  Here the rules are bent so
+    that the whole engine runs on the others: the TMA + tcgen05 product for every matrix (batches of 12), the
+    balanced decode attention (with the separate q/k kernel before it), and K slices / key splits that meet in
+    clusters.  Freed pages are poisoned between batches."""
+    from starter_b200.csrc.ops import get_ops
+    ops = get_ops(verbose=False)
+    if route == "stream":
+        monkeypatch.setattr(ops, "STREAM_MIN_WORK", 0)
+        monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 0)
+        batch = 12
+    elif route == "balanced":
+        monkeypatch.setattr(ops, "decode_resident", lambda *a: 0)
+        batch = 5
+    else:
+        monkeypatch.setattr(ops, "skinny_splits", lambda blocks, K: 3)
+        monkeypatch.setattr(ops, "decode_splits", lambda *a: 3)
+        batch = 4
+    folder, dtype = tiny_folders["M"], "bfloat16"
+    lengths = (5, 150, 77, 1, 64, 65, 33, 90, 129, 12, 70, 200, 3)
+    seqs = random_tokens(TINY["M"]["vocab_size"], lengths, seed=19)
+    ref = plain_logits(folder, seqs, dtype)
+    sess = make_session(folder, dtype, max_tokens=64 * 40, max_seqs=batch, max_step_tokens=96)
+    before = ops.launches
+    assert_close(run_ragged_batches(sess, seqs, batch_size=batch, poison=True), ref, dtype, f"ragged batches, route {route}")
+    assert ops.launches > before
+    assert sess.cache.slots.n_held == 0
