@@ -176,3 +176,37 @@ def load(verbose: bool = True) -> ctypes.CDLL:
         except OSError as exc:
             raise BuildError(f"{path} could not be loaded: {exc}") from None
     return _LIB
+
+
+def register_report(names=()) -> int:
+    """Registers and spills of every kernel, as ptxas reports them (``python -m starter_b200.csrc.build [file.cu ...]``).
+    The decode product sits exactly at the register count that four 8-warp blocks per SM allow: read this after
+    every change to it."""
+    import re
+    nvcc = find_nvcc()
+    worst = 0
+    for src in sources():
+        if names and src.name not in names:
+            continue
+        cmd = [nvcc, *ARCH_FLAGS, *NVCC_FLAGS, "-Xptxas", "-v", "-I", str(HERE), "-c", str(src), "-o", os.devnull]
+        proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True)
+        if proc.returncode != 0:
+            raise BuildError(f"nvcc failed on {src.name}:\n{proc.stdout}")
+        kernel, spills = None, (0, 0)
+        for line in proc.stdout.splitlines():
+            m = re.search(r"Compiling entry function '(\S+)'", line)
+            if m:
+                kernel = subprocess.run(["c++filt", m.group(1)], stdout=subprocess.PIPE, text=True).stdout.strip() or m.group(1)
+                kernel = kernel.split("(")[0]
+            m = re.search(r"(\d+) bytes spill stores, (\d+) bytes spill loads", line)
+            if m:
+                spills = (int(m.group(1)), int(m.group(2)))
+            m = re.search(r"Used (\d+) registers", line)
+            if m and kernel:
+                print(f"{src.name:26s} {kernel[:78]:78s} {int(m.group(1)):4d} registers  spill {spills[0]}/{spills[1]} bytes")
+                worst = max(worst, spills[0], spills[1])
+    return worst
+
+
+if __name__ == "__main__":
+    register_report(tuple(sys.argv[1:]))
