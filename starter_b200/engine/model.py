@@ -27,12 +27,12 @@ class DecoderModel:
         def load(name):
             return checkpoint.load(name, dtype, device)
 
-        self.embedding = ops.prepare_matrix(load(names.embedding))
+        self.embedding = load(names.embedding).contiguous()   # a table to gather rows from: no product reads it ...
         if checkpoint.has(names.lm_head):
             # engine/model.py:103-107: an lm_head in the file is used even when the config ties.
             self.lm_head = ops.prepare_matrix(load(names.lm_head))
         elif spec.tie_embeddings:
-            self.lm_head = self.embedding
+            self.lm_head = ops.prepare_matrix(self.embedding)   # ... unless it is the output head as well (same tensor)
         else:
             raise WeightsError(f"{checkpoint.where}: {names.lm_head} is missing and the embeddings are not tied")
         norm_cls = part_class("norm", spec.final_norm.kind)
