@@ -91,3 +91,21 @@ def test_stop_tokens_and_slot_reuse(tiny_folders):
         tokens_agree(got, want, cfg, tensors, prompts, "float32", 1e-4)
         assert eng.session.cache.slots.n_held == 0
         eng.session.cache.check()
+
+
+@pytest.mark.parametrize("graphs", [False, True])
+@pytest.mark.parametrize("name", ["M", "N"])
+def test_greedy_on_the_tensor_core_kernels(tiny_folders, name, graphs):
+    """The configurations whose head sizes put prefill and decode on the tensor-core attention kernels (the decode
+    one with the q/k preparation inside), with unequal prompts, a window in M, replayed graphs and not."""
+    dtype = "bfloat16"
+    prompts = random_tokens(TINY[name]["vocab_size"], (70, 5, 131, 1), seed=23)
+    cfg, tensors = plain.read_folder(tiny_folders[name])
+    want = plain.generate(cfg, tensors, prompts, 10, dtype)
+    eng = Engine(tiny_folders[name], dtype=dtype, max_batch=4, max_context=192, use_graphs=graphs)
+    steps = list(eng.generate(prompts, 10))
+    got = [[s[b] for s in steps] for b in range(len(prompts))]
+    tokens_agree(got, want, cfg, tensors, prompts, dtype, 2e-2)
+    again = list(eng.generate(prompts[:2], 10))                             # fewer requests, slots used again
+    assert [[s[b] for s in again] for b in range(2)] == got[:2]
+    assert eng.session.cache.slots.n_held == 0
