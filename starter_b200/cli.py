@@ -51,8 +51,9 @@ def _random_weights(args) -> int:
     from .weights import write_model_folder
     config = config_from_dict(json.loads(Path(args.config).read_text()))
     dtype = {"bfloat16": torch.bfloat16, "float32": torch.float32}[args.dtype]
-    write_model_folder(config, args.seed, args.out, dtype=dtype)
-    print(f"wrote {args.out}/config.json and {args.out}/model.safetensors")
+    write_model_folder(config, args.seed, args.out, dtype=dtype, shards=args.shards)
+    files = "model.safetensors" if args.shards <= 1 else f"{args.shards} model-*-of-*.safetensors shards"
+    print(f"wrote {args.out}/config.json and {args.out}/{files}")
     return 0
 
 
@@ -66,7 +67,7 @@ def build_parser() -> argparse.ArgumentParser:
     sub = p.add_subparsers(dest="command", required=True)
 
     g = sub.add_parser("generate", help="continue prompts given as token ids")
-    g.add_argument("--model", required=True, help="model_path: folder with config.json and model.safetensors")
+    g.add_argument("--model", required=True, help="model_path: folder with config.json and model.safetensors (or its shards)")
     g.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
     g.add_argument("--input-ids", help='prompts as token ids, sequences separated by ";": "1,2,3;4,5"')
     g.add_argument("--input-file", help="JSON file with a list of token-id lists")
@@ -86,6 +87,7 @@ def build_parser() -> argparse.ArgumentParser:
     r.add_argument("--seed", type=int, default=0)
     r.add_argument("--out", required=True)
     r.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    r.add_argument("--shards", type=int, default=1, help="split the tensors over this many safetensors files")
     r.set_defaults(func=_random_weights)
 
     t = sub.add_parser("replay", help="feed given token ids step by step and write logits (see bin/trace_run)")

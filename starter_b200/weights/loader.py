@@ -1,11 +1,14 @@
 """Weights by tensor name, checked against what the model expects.
 
-The reference pops each tensor by its name, fuses q/k/v and gate/up, ties the
-output head to the embedding when the file has no ``lm_head.weight``, and
-rejects leftovers (engine/model.py:100-128); each fault raises on its own.
-Here the model's parts declare the tensors they want, the file is compared
-with that list once, and a single error names every missing tensor, every
-unexpected tensor and every wrong shape.
+The reference reads every ``*.safetensors`` shard of the folder, sorted, into
+one dict by name (engine/model.py:67-75), pops each tensor by its name, fuses
+q/k/v and gate/up, ties the output head to the embedding when the file has no
+``lm_head.weight``, and rejects leftovers (engine/model.py:100-128); each
+fault raises on its own.  Here the shards are mapped, not read (a tensor is
+materialised when it is asked for), the model's parts declare the tensors
+they want, the folder is compared with that list once, and a single error
+names every missing tensor, every unexpected tensor, every wrong shape and
+every tensor that two shards both hold.
 
 Dtypes: a tensor stored in bfloat16 stays bfloat16 and one stored in 32-bit
 stays 32-bit for a bfloat16 run; a float32 run widens everything; integer
@@ -48,12 +51,14 @@ def expected_tensors(spec, names) -> Tuple[Dict[str, Tuple[int, ...]], Dict[str,
     return required, optional
 
 
-def check_tensors(found: Dict[str, Tuple[int, ...]], required, optional, where: str) -> None:
+def check_tensors(found: Dict[str, Tuple[int, ...]], required, optional, where: str, duplicates=None) -> None:
+    """``duplicates``: {name: [files that hold it]} for names stored more than once."""
+    duplicates = duplicates or {}
     missing = sorted(n for n in required if n not in found)
     unexpected = sorted(n for n in found if n not in required and n not in optional)
     wrong = sorted((n, found[n], want) for n, want in {**optional, **required}.items()
                    if n in found and tuple(found[n]) != tuple(want))
-    if not (missing or unexpected or wrong):
+    if not (missing or unexpected or wrong or duplicates):
         return
     lines = [f"{where} does not match the model:"]
     if missing:
@@ -63,6 +68,9 @@ def check_tensors(found: Dict[str, Tuple[int, ...]], required, optional, where: 
     if wrong:
         lines.append(f"  wrong shape ({len(wrong)}): "
                      + ", ".join(f"{n} is {list(have)}, expected {list(want)}" for n, have, want in wrong))
+    if duplicates:
+        lines.append(f"  stored more than once ({len(duplicates)}): "
+                     + ", ".join(f"{n} in {' and '.join(files)}" for n, files in sorted(duplicates.items())))
     raise WeightsError("\n".join(lines))
 
 
@@ -77,8 +85,50 @@ def to_run_dtype(t: torch.Tensor, run_dtype: torch.dtype, name: str) -> torch.Te
                        "(run with dtype float32 to widen it)")
 
 
+class ShardedSource:
+    """Every ``*.safetensors`` file of a folder, sorted by name, as one source of tensors by name.
+
+    No index file is read: the shards' own headers say what each holds, as in
+    the reference (engine/model.py:67-75).  There a name in two shards is
+    silently taken from the later one; here it is kept in ``duplicates`` and
+    reported with the other faults.
+    """
+
+    def __init__(self, folder):
+        self.folder = Path(folder)
+        paths = sorted(self.folder.glob("*.safetensors"))
+        if not paths:
+            raise FileNotFoundError(f"no *.safetensors file in {self.folder}: a model folder holds config.json and "
+                                    "model.safetensors (or its shards)")
+        self.files = []
+        self.entries: Dict[str, Tuple[torch.dtype, Tuple[int, ...]]] = {}
+        self.duplicates: Dict[str, list] = {}
+        self._home: Dict[str, SafetensorsFile] = {}
+        try:
+            for path in paths:
+                shard = SafetensorsFile(path)
+                self.files.append(shard)
+                for name, entry in shard.entries.items():
+                    if name in self._home:
+                        self.duplicates.setdefault(name, [self._home[name].path.name]).append(path.name)
+                        continue
+                    self.entries[name] = entry
+                    self._home[name] = shard
+        except Exception:
+            self.close()
+            raise
+
+    def get(self, name: str) -> torch.Tensor:
+        return self._home[name].get(name)
+
+    def close(self) -> None:
+        for shard in self.files:
+            shard.close()
+        self.files, self.entries, self._home = [], {}, {}
+
+
 class Checkpoint:
-    """A source of tensors by name: a mapped model.safetensors, or anything with ``entries`` and ``get``."""
+    """A source of tensors by name: a folder's mapped shards, or anything with ``entries`` and ``get``."""
 
     def __init__(self, source, where: str):
         self.source = source
@@ -86,15 +136,17 @@ class Checkpoint:
 
     @classmethod
     def open(cls, folder) -> "Checkpoint":
-        path = Path(folder) / "model.safetensors"
-        return cls(SafetensorsFile(path), str(path))
+        source = ShardedSource(folder)
+        where = str(source.files[0].path) if len(source.files) == 1 else \
+            f"{folder} ({len(source.files)} safetensors files)"
+        return cls(source, where)
 
     def shapes(self) -> Dict[str, Tuple[int, ...]]:
         return {name: tuple(shape) for name, (_, shape) in self.source.entries.items()}
 
     def check(self, spec, names) -> None:
         required, optional = expected_tensors(spec, names)
-        check_tensors(self.shapes(), required, optional, self.where)
+        check_tensors(self.shapes(), required, optional, self.where, getattr(self.source, "duplicates", None))
 
     def has(self, name: str) -> bool:
         return name in self.source.entries

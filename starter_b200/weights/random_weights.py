@@ -50,10 +50,27 @@ class RandomSource:
         return (MATRIX_STD * noise).to(self.dtype)
 
 
-def write_model_folder(config, seed: int, folder, dtype: torch.dtype = torch.bfloat16) -> Path:
-    """Write ``config.json`` and ``model.safetensors`` for ``config`` with seeded random weights."""
+def write_model_folder(config, seed: int, folder, dtype: torch.dtype = torch.bfloat16, shards: int = 1) -> Path:
+    """Write ``config.json`` and ``model.safetensors`` for ``config`` with seeded random weights.
+
+    ``shards`` > 1 writes ``model-0000i-of-0000n.safetensors`` files instead, the
+    tensors dealt out in order in runs of about equal bytes, the way published
+    checkpoints are laid out (no index file: the loader needs none).
+    """
     folder = Path(folder)
     save_config(config, folder)
     source = RandomSource(config, seed, dtype=dtype)
-    write_safetensors(folder / "model.safetensors", list(source.entries.items()), source.get)
+    items = list(source.entries.items())
+    if shards <= 1:
+        write_safetensors(folder / "model.safetensors", items, source.get)
+        return folder
+    sizes = [torch.Size(shape).numel() for _, (_, shape) in items]
+    per_shard, groups, run = sum(sizes) / shards, [[]], 0
+    for item, size in zip(items, sizes):
+        if run >= per_shard * len(groups) and len(groups) < shards:
+            groups.append([])
+        groups[-1].append(item)
+        run += size
+    for i, group in enumerate(groups):
+        write_safetensors(folder / f"model-{i + 1:05d}-of-{len(groups):05d}.safetensors", group, source.get)
     return folder

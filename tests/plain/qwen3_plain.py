@@ -36,13 +36,15 @@ def _rounder(mode: str):
 
 
 def read_folder(folder):
-    """config.json as a dict and every tensor of model.safetensors widened to float32."""
+    """config.json as a dict and every tensor of every *.safetensors file of the folder, sorted
+    (engine/model.py:67-75), widened to float32."""
     folder = Path(folder)
     cfg = json.loads((folder / "config.json").read_text())
     tensors = {}
-    with safe_open(str(folder / "model.safetensors"), framework="pt", device="cpu") as f:
-        for name in f.keys():
-            tensors[name] = f.get_tensor(name).to(torch.float32)
+    for path in sorted(folder.glob("*.safetensors")):
+        with safe_open(str(path), framework="pt", device="cpu") as f:
+            for name in f.keys():
+                tensors[name] = f.get_tensor(name).to(torch.float32)
     return cfg, tensors
 
 

@@ -122,3 +122,83 @@ def test_random_weights_are_a_function_of_seed_and_name(tmp_path):
     bigger = config_from_dict(dict(tiny_raw("A"), num_hidden_layers=3))
     src = RandomSource(bigger, 7)
     assert torch.equal(src.get("model.layers.0.mlp.up_proj.weight"), a["model.layers.0.mlp.up_proj.weight"])
+
+
+# ---- checkpoints in several files (engine/model.py:67-75 reads every *.safetensors of the folder, sorted) ----
+
+def _split_into_shards(src_folder, dst_folder, groups):
+    """Write the tensors of ``src_folder`` into len(groups) + 1 shard files: ``groups`` are lists of
+    predicates' names; what no group takes goes to the last file."""
+    tensors = read_all(src_folder / "model.safetensors")
+    (dst_folder / "config.json").write_text((src_folder / "config.json").read_text())
+    taken = set()
+    n = len(groups) + 1
+    for i, names in enumerate(groups):
+        save_file({k: tensors[k] for k in names}, str(dst_folder / f"model-{i + 1:05d}-of-{n:05d}.safetensors"))
+        taken |= set(names)
+    save_file({k: v for k, v in tensors.items() if k not in taken}, str(dst_folder / f"model-{n:05d}-of-{n:05d}.safetensors"))
+    return tensors
+
+
+def _odd_split(tensors):
+    """The embedding alone in one file; layer 1 cut across two files."""
+    layer1 = sorted(k for k in tensors if k.startswith("model.layers.1."))
+    second = [k for k in tensors if k.startswith("model.layers.0.")] + layer1[:len(layer1) // 2]
+    return [["model.embed_tokens.weight"], second]
+
+
+def test_sharded_folder_gives_the_same_logits(tiny_folders, tmp_path):
+    from conftest import random_tokens
+    from helpers import make_session, run_whole
+    tensors = read_all(tiny_folders["B"] / "model.safetensors")
+    _split_into_shards(tiny_folders["B"], tmp_path, _odd_split(tensors))
+    assert len(list(tmp_path.glob("*.safetensors"))) == 3
+    seqs = random_tokens(TINY["B"]["vocab_size"], (5, 70, 33), seed=3)
+    outs = []
+    for folder in (tiny_folders["B"], tmp_path):
+        sess = make_session(folder, "float32", ops=EmulatedOps(), max_tokens=64 * 6, max_seqs=3)
+        outs.append(run_whole(sess, seqs, together=True))
+    assert all(torch.equal(a, b) for a, b in zip(*outs))
+
+
+def test_sharded_folder_faults_are_listed_together(tiny_folders, tmp_path):
+    tensors = _split_into_shards(tiny_folders["B"], tmp_path, _odd_split(read_all(tiny_folders["B"] / "model.safetensors")))
+    # a fourth file: one tensor a second time, one that nobody wants; and one tensor goes missing from shard 2
+    save_file({"model.embed_tokens.weight": tensors["model.embed_tokens.weight"],
+               "model.layers.0.mlp.gate_proj.bias": torch.zeros(224, dtype=torch.bfloat16)},
+              str(tmp_path / "model-extra.safetensors"))
+    second = read_all(tmp_path / "model-00002-of-00003.safetensors")
+    del second["model.layers.0.self_attn.k_norm.weight"]
+    save_file(second, str(tmp_path / "model-00002-of-00003.safetensors"))
+    with pytest.raises(WeightsError) as err:
+        DecoderModel.from_folder(tmp_path, runtime())
+    text = str(err.value)
+    assert "4 safetensors files" in text
+    assert "missing (1)" in text and "model.layers.0.self_attn.k_norm.weight" in text
+    assert "unexpected (1)" in text and "gate_proj.bias" in text
+    assert "stored more than once (1)" in text
+    assert "model.embed_tokens.weight in model-00001-of-00003.safetensors and model-extra.safetensors" in text
+
+
+def test_folder_without_shards(tmp_path, tiny_folders):
+    (tmp_path / "config.json").write_text((tiny_folders["A"] / "config.json").read_text())
+    with pytest.raises(FileNotFoundError, match=r"no \*\.safetensors file"):
+        DecoderModel.from_folder(tmp_path, runtime())
+
+
+def test_random_weights_in_shards_equal_the_single_file(tmp_path):
+    cfg = config_from_dict(tiny_raw("B"))
+    write_model_folder(cfg, 5, tmp_path / "one")
+    write_model_folder(cfg, 5, tmp_path / "three", shards=3)
+    files = sorted((tmp_path / "three").glob("*.safetensors"))
+    assert [f.name for f in files] == [f"model-0000{i}-of-00003.safetensors" for i in (1, 2, 3)]
+    one = read_all(tmp_path / "one" / "model.safetensors")
+    three = {}
+    for f in files:
+        part = read_all(f)
+        assert part and not (part.keys() & three.keys())
+        three.update(part)
+    assert one.keys() == three.keys() and all(torch.equal(one[k], three[k]) for k in one)
+    a = DecoderModel.from_folder(tmp_path / "one", runtime())
+    b = DecoderModel.from_folder(tmp_path / "three", runtime())
+    assert torch.equal(a.blocks[2].ff.w_gate_up, b.blocks[2].ff.w_gate_up) and torch.equal(a.lm_head, b.lm_head)
