@@ -101,7 +101,16 @@ def build_parser() -> argparse.ArgumentParser:
 
 def main(argv=None) -> int:
     args = build_parser().parse_args(argv)
-    return args.func(args)
+    from .csrc.build import BuildError
+    from .engine.generate import GenerationError
+    from .engine.step import StepError
+    from .weights import SafetensorsError, WeightsError
+    try:
+        return args.func(args)
+    except (BuildError, GenerationError, StepError, WeightsError, SafetensorsError, FileNotFoundError) as exc:
+        # what a user can act on comes as one message, not as a traceback
+        print(f"starter_b200: {exc}", file=sys.stderr)
+        return 1
 
 
 if __name__ == "__main__":

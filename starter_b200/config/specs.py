@@ -81,6 +81,10 @@ class ModelSpec:
     ``schedule`` lists layer indices in execution order; an index may appear
     more than once: the layer then runs again with the same weights, and each occurrence keeps
     a cache entry of its own.
+
+    Three optional constants of the outer model, None where an architecture has none (Qwen3 has
+    none): ``embedding_scale`` multiplies the embedded rows, ``logit_scale`` the logits, and
+    ``logit_softcap`` c turns a logit x into c * tanh(x / c), after the scale.
     """
 
     hidden_size: int
@@ -89,6 +93,9 @@ class ModelSpec:
     final_norm: Any
     tie_embeddings: bool
     schedule: Tuple[int, ...] = field(default=())
+    embedding_scale: Optional[float] = None
+    logit_scale: Optional[float] = None
+    logit_softcap: Optional[float] = None
 
     def execution_order(self) -> Tuple[int, ...]:
         return self.schedule if self.schedule else tuple(range(len(self.layers)))

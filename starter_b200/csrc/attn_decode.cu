@@ -36,6 +36,7 @@ namespace cg = cooperative_groups;
 #define AD_WARPS 4
 #define AD_KEYS_PER_WARP (SB_PAGE / AD_WARPS)  // 16
 #define AD_MAX_CLUSTER 8
+#define AD_MAX_DEVICES 64     // devices whose per-device set-up this file remembers
 
 // What the fused preparation needs besides the cache.  qkv [rows, (n_heads + 2 * n_kv_heads) * D], or
 // [rows, n_heads * D] when store_kv is 0 (a layer that reads another layer's cache); norm weights
@@ -471,11 +472,14 @@ static int launch_decode_staged(const void* q, void* out, SbBatch batch, SbKV kv
     const int pipe_bytes = AD_WARPS * AD_STAGES * 2 * AD_KEYS_PER_WARP * D * 2;
     const int merge_bytes = (AD_WARPS * 16 * D + 2 * AD_WARPS * 16 + 16 * D + 32) * 4;
     const int smem = 16 * D * 2 + (pipe_bytes > merge_bytes ? pipe_bytes : merge_bytes);
-    static bool configured = false;
-    if (!configured) {
+    // the attribute belongs to the kernel as loaded on one device: once per device
+    static bool configured[AD_MAX_DEVICES] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= AD_MAX_DEVICES) return (int)cudaErrorInvalidDevice;
+    if (!configured[device]) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel<D, FUSED, AD_STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured[device] = true;
     }
     const int cluster_merge = n_splits >= 2 && n_splits <= AD_MAX_CLUSTER;
     cudaLaunchConfig_t config = {};
@@ -512,22 +516,32 @@ static int launch_decode_staged(const void* q, void* out, SbBatch batch, SbKV kv
 template <int D, bool FUSED>
 static int launch_decode(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale, int window, int n_splits,
                          float* partial, int* counters, SbFusedQK fused, cudaStream_t stream) {
-    static int sm_count = 0;
-    if (sm_count == 0) {
-        int device = 0;
-        if (cudaGetDevice(&device) != cudaSuccess ||
-            cudaDeviceGetAttribute(&sm_count, cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
-            sm_count = 1;
-    }
+    static int sm_counts[AD_MAX_DEVICES] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= AD_MAX_DEVICES) return (int)cudaErrorInvalidDevice;
+    if (sm_counts[device] == 0 &&
+        cudaDeviceGetAttribute(&sm_counts[device], cudaDevAttrMultiProcessorCount, device) != cudaSuccess)
+        sm_counts[device] = 1;
+    const int sm_count = sm_counts[device];
     const long long blocks = (long long)batch.n_seqs * kv.n_kv_heads * n_splits;
     if (blocks <= sm_count)
         return launch_decode_staged<D, FUSED, 4>(q, out, batch, kv, n_heads, scale, window, n_splits, partial, counters, fused, stream);
     return launch_decode_staged<D, FUSED, 3>(q, out, batch, kv, n_heads, scale, window, n_splits, partial, counters, fused, stream);
 }
 
+// Most splits whose merge fits: the last block of a (sequence, kv head) keeps two floats per (query head of the
+// group, split) in the shared memory of its page pipeline (the smallest pipeline: three stages).
+static int decode_max_splits(int group, int head_dim) {
+    const int pipe_bytes = AD_WARPS * 3 * 2 * AD_KEYS_PER_WARP * head_dim * 2;
+    const int merge_bytes = (AD_WARPS * 16 * head_dim + 2 * AD_WARPS * 16 + 16 * head_dim + 32) * 4;
+    const int most = (pipe_bytes > merge_bytes ? pipe_bytes : merge_bytes) / (2 * (int)sizeof(float) * (group > 0 ? group : 1));
+    return most < 65535 ? most : 65535;
+}
+
 static bool decode_shape_ok(const SbBatch& batch, const SbKV& kv, int n_heads, int n_splits) {
-    return batch.n_rows == batch.n_seqs && n_heads % kv.n_kv_heads == 0 && n_heads / kv.n_kv_heads <= 16 && n_splits >= 1 &&
-           n_splits <= 65535 && kv.n_kv_heads <= 65535 && (kv.head_dim == 64 || kv.head_dim == 128);
+    if (kv.n_kv_heads <= 0 || n_heads <= 0 || kv.n_kv_heads > 65535 || (kv.head_dim != 64 && kv.head_dim != 128)) return false;
+    if (batch.n_rows != batch.n_seqs || n_heads % kv.n_kv_heads != 0 || n_heads / kv.n_kv_heads > 16) return false;
+    return n_splits >= 1 && (n_splits <= AD_MAX_CLUSTER || n_splits <= decode_max_splits(n_heads / kv.n_kv_heads, kv.head_dim));
 }
 
 extern "C" {
@@ -536,6 +550,12 @@ extern "C" {
 // (none with up to 8 splits, which merge through shared memory).
 long long sb_attn_decode_scratch_floats(int n_seqs, int n_heads, int head_dim, int n_splits) {
     return n_splits > AD_MAX_CLUSTER ? (long long)n_seqs * n_heads * n_splits * (head_dim + 2) : 0;
+}
+
+// Most splits a call may ask for (more would not fit the merge's shared memory and is refused).
+int sb_attn_decode_max_splits(int n_heads, int n_kv_heads, int head_dim) {
+    if (n_heads <= 0 || n_kv_heads <= 0 || n_heads % n_kv_heads) return 0;
+    return decode_max_splits(n_heads / n_kv_heads, head_dim);
 }
 
 // One new token per sequence (rows == sequences).  q, out [rows, n_heads * head_dim] bfloat16.
@@ -585,10 +605,24 @@ extern "C" {
 
 const char* sb_attn_decode_noalloc_error(void) { return sb_noalloc_message; }
 
+void* sb_attn_decode_noalloc_scratch(void) {
+    int device = -1;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= SB_NOALLOC_MAX_DEVICES) return nullptr;
+    return sb_noalloc_device_ptr[device];
+}
+
 int sb_attn_decode_noalloc(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale, int window,
                            int n_splits, cudaStream_t stream) {
     sb_noalloc_message[0] = 0;
     if (batch.n_seqs <= 0) return 0;
+    if (kv.n_kv_heads <= 0 || n_heads <= 0 || n_splits < 1) return (int)cudaErrorInvalidValue;
+    if (n_splits > AD_MAX_CLUSTER && n_splits > sb_attn_decode_max_splits(n_heads, kv.n_kv_heads, kv.head_dim)) {
+        snprintf(sb_noalloc_message, sizeof(sb_noalloc_message),
+                 "sb_attn_decode_noalloc: %d splits are more than the %d whose merge fits a block's shared memory "
+                 "at %d query heads per kv head", n_splits, sb_attn_decode_max_splits(n_heads, kv.n_kv_heads, kv.head_dim),
+                 n_heads / kv.n_kv_heads);
+        return SB_NOALLOC_TOO_LARGE;
+    }
     const long long counters_needed = (long long)batch.n_seqs * kv.n_kv_heads;
     const long long floats_needed = sb_attn_decode_scratch_floats(batch.n_seqs, n_heads, kv.head_dim, n_splits);
     if (counters_needed > SB_NOALLOC_MAX_COUNTERS || floats_needed > SB_NOALLOC_MAX_FLOATS) {

@@ -18,9 +18,11 @@
 //    merge through shared memory and use no scratch),
 //    n_seqs * n_heads * n_splits * (head_dim + 2) floats; a call that needs more is refused
 //    with SB_NOALLOC_TOO_LARGE and sb_attn_decode_noalloc_error() says what was asked for.
-//  * The first call on a device looks the array's device address up (cudaGetSymbolAddress)
-//    and sets the kernel's shared-memory limit.  Make that first call before any stream
-//    capture begins on that device.
+//  * The first call on a device (with that device current) looks the array's address on that
+//    device up (cudaGetSymbolAddress) and sets the kernel's shared-memory limit there; both are
+//    remembered per device.  Make that first call before any stream capture begins on that device.
+//  * More splits than the merge step has shared memory for (two floats per split and query head of
+//    a group: 384 splits at 16 heads per kv head and head size 64) are refused with SB_NOALLOC_TOO_LARGE.
 //  * All calls share the one array, and it keeps whatever the last call left in it.  The
 //    entry point clears the counters on the given stream before each launch; the partial
 //    results need no clearing (every value read was written by the same launch).  Two calls
@@ -47,5 +49,9 @@ int sb_attn_decode_noalloc(const void* q, void* out, SbBatch batch, SbKV kv, int
 
 // Text of the last negative result on the calling thread ("" if there was none).
 const char* sb_attn_decode_noalloc_error(void);
+
+// For tests and debuggers: the array's address on the current device (counters first, then the partial
+// results), or null before the first call there.  Not needed to use the entry point.
+void* sb_attn_decode_noalloc_scratch(void);
 
 }

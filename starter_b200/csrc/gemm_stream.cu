@@ -24,95 +24,11 @@
 #include <mutex>
 #include <unordered_map>
 
-#include "common.cuh"
+#include "tc_utils.cuh"
 
-#define SB_STATUS_TIMEOUT 4
 #define ST_BM 128               // rows of W per tile
 #define ST_BK 64                // columns of K per stage: 128 bytes, one swizzle span
 #define ST_THREADS 192
-#define ST_WAIT_LIMIT (1ll << 31)  // clock cycles a wait may last (about a second)
-
-// ---- PTX wrappers -------------------------------------------------------------------------------
-
-__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
-    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
-                 : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-// Waits for the phase of the given parity; false if it gave up (time limit, or another role aborted).
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag, int* status) {
-    if (mbar_try_wait(bar, parity)) return true;
-    const long long t0 = clock64();
-    while (!mbar_try_wait(bar, parity)) {
-        if (*abort_flag) return false;
-        if (clock64() - t0 > ST_WAIT_LIMIT) {
-            *abort_flag = 1;
-            atomicOr(status, SB_STATUS_TIMEOUT);
-            return false;
-        }
-        __nanosleep(32);
-    }
-    return true;
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y) : "memory");
-}
-__device__ __forceinline__ void tmem_alloc(uint32_t* dst_smem, uint32_t cols) {
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(dst_smem)), "r"(cols) : "memory");
-    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void tmem_dealloc(uint32_t addr, uint32_t cols) {
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(addr), "r"(cols) : "memory");
-}
-__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
-__device__ __forceinline__ void tc_commit(uint64_t* bar) {
-    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
-}
-__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\ttcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate) : "memory");
-}
-// 16 consecutive 32-bit columns of this warp's 32 lanes of tensor memory.
-__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
-    uint32_t r[16];
-    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
-                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
-                   "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
-                 : "r"(taddr));
-    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
-}
-
-// Shared-memory descriptor of a K-major bfloat16 tile [rows][64] written by TMA with the 128-byte
-// swizzle: rows are 128 bytes apart, groups of eight rows 1024 bytes apart.
-__device__ __forceinline__ uint64_t umma_desc(const void* tile) {
-    uint64_t d = 0;
-    d |= (uint64_t)((smem_u32(tile) & 0x3FFFF) >> 4);   // start address, bits [0,14)
-    d |= (uint64_t)1 << 16;                             // leading byte offset (unused for this layout)
-    d |= (uint64_t)(1024 >> 4) << 32;                   // stride byte offset, bits [32,46)
-    d |= (uint64_t)1 << 46;                             // descriptor version of sm_100
-    d |= (uint64_t)2 << 61;                             // layout: 128-byte swizzle
-    return d;
-}
-// Instruction descriptor: bfloat16 x bfloat16 -> float, both operands K-major, M = 128, N = n.
-__device__ __forceinline__ uint32_t umma_idesc(int n) {
-    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(ST_BM >> 4) << 24);
-}
 
 __device__ __forceinline__ float silu_mul_rounded(float g, float u) {
     // engine/kernels/gemm.py:116-121
@@ -131,9 +47,12 @@ struct StreamArgs {
     int M, n_out, K;
     int n_tiles, k_blocks, max_parts;
     int out_f32;
-    long long* timeline;  // when not null: [block][16] globaltimer stamps of the block's milestones (for tuning)
+#ifdef SB_TIMELINE
+    long long* timeline;  // tuning builds only: [block][16] globaltimer stamps of the block's milestones
+#endif
 };
 
+#ifdef SB_TIMELINE
 __device__ __forceinline__ void stamp(const StreamArgs& args, int slot) {
     if (args.timeline) {
         long long t;
@@ -141,6 +60,9 @@ __device__ __forceinline__ void stamp(const StreamArgs& args, int slot) {
         args.timeline[blockIdx.x * 16 + slot] = t;
     }
 }
+#else
+#define stamp(args, slot) ((void)0)
+#endif
 
 // Units [u0, u1) of block c out of P, with U units in all.
 __device__ __forceinline__ long long unit_begin(long long c, long long U, long long P) { return c * U / P; }
@@ -216,7 +138,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
         bool ok = true;
         for (long long u = u0 + pre; u < u1 && ok; ++u) {
             const int tile = (int)(u / args.k_blocks), kb = (int)(u % args.k_blocks);
-            ok = mbar_wait(&empty[stage], phase ^ 1, abort_flag, args.status);
+            ok = mbar_wait<true>(&empty[stage], phase ^ 1, abort_flag, args.status);
             if (!ok) break;
             mbar_expect_tx(&full[stage], N_A * A_BYTES + B_BYTES);
             tma_load_2d(a_s + (stage * N_A) * A_BYTES, &map_w, kb * ST_BK, tile * ST_BM, &full[stage]);
@@ -244,20 +166,20 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int kb0 = (int)(u % args.k_blocks);
             const int n_kb = (int)min((long long)(args.k_blocks - kb0), u1 - u);
             const int buf = item & 1;
-            ok = mbar_wait(&acc_empty[buf], acc_phase[buf] ^ 1, abort_flag, args.status);
+            ok = mbar_wait<true>(&acc_empty[buf], acc_phase[buf] ^ 1, abort_flag, args.status);
             if (!ok) break;
             acc_phase[buf] ^= 1;
             tc_fence_after();
             const uint32_t d_tmem = tmem_base + buf * ACC_COLS;
             for (int i = 0; i < n_kb && ok; ++i) {
-                ok = mbar_wait(&full[stage], phase, abort_flag, args.status);
+                ok = mbar_wait<true>(&full[stage], phase, abort_flag, args.status);
                 if (!ok) break;
                 if (item == 0 && i == 0) stamp(args, 5);
                 tc_fence_after();
-                const uint64_t b_desc = umma_desc(b_s + stage * B_BYTES);
+                const uint64_t b_desc = desc_k_major(b_s + stage * B_BYTES);
 #pragma unroll
                 for (int a = 0; a < N_A; ++a) {
-                    const uint64_t a_desc = umma_desc(a_s + (stage * N_A + a) * A_BYTES);
+                    const uint64_t a_desc = desc_k_major(a_s + (stage * N_A + a) * A_BYTES);
 #pragma unroll
                     for (int k = 0; k < ST_BK / 16; ++k)   // 16 columns = 32 bytes = 2 descriptor units per step
                         tc_mma(d_tmem + a * BN, a_desc + 2 * k, b_desc + 2 * k, idesc, (i > 0 || k > 0) ? 1u : 0u);
@@ -283,7 +205,7 @@ gemm_stream_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_const
             const int buf = item & 1;
             const bool whole = n_kb == args.k_blocks;
             // One thread waits and tells the others, so that all four warps go on or all four leave.
-            if (threadIdx.x == 64) wait_flag[buf] = mbar_wait(&acc_full[buf], acc_phase[buf], abort_flag, args.status) ? 1 : 0;
+            if (threadIdx.x == 64) wait_flag[buf] = mbar_wait<true>(&acc_full[buf], acc_phase[buf], abort_flag, args.status) ? 1 : 0;
             asm volatile("bar.sync 1, 128;" ::: "memory");
             ok = wait_flag[buf] != 0;
             if (!ok) break;
@@ -469,8 +391,10 @@ int sb_gemm_stream_plan(int n_out, int K, int n_sms, int* grid, int* n_tiles, in
 
 // A [M, K], W [n_out, K] (or [2 * n_out, K], gate rows first, with gate_up), C [M, n_out] bfloat16 or float.
 // M <= 64, K a multiple of 8.  grid, max_parts from sb_gemm_stream_plan.
+#ifdef SB_TIMELINE
 static long long* stream_timeline = nullptr;
 void sb_gemm_stream_timeline(long long* buffer) { stream_timeline = buffer; }
+#endif
 
 int sb_gemm_stream(const void* A, const void* W, void* C, int M, int n_out, int K, int gate_up, int out_f32, int grid,
                    int max_parts, float* partial, int* counters, int* status, cudaStream_t stream) {
@@ -491,7 +415,9 @@ int sb_gemm_stream(const void* A, const void* W, void* C, int M, int n_out, int 
     args.k_blocks = (K + ST_BK - 1) / ST_BK;
     args.max_parts = max_parts;
     args.out_f32 = out_f32;
+#ifdef SB_TIMELINE
     args.timeline = stream_timeline;
+#endif
     if (gate_up) {
         if (bn == 16) return launch_stream<16, true, 6>(mw, mw2, ma, args, grid, stream);
         return launch_stream<32, true, 5>(mw, mw2, ma, args, grid, stream);

@@ -10,6 +10,7 @@ the compiled library, ``get_ops`` raises.
 
 from __future__ import annotations
 
+import contextlib
 import ctypes
 import weakref
 import os
@@ -92,7 +93,7 @@ class Ops:
                                      c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
             "sb_sample": [c_void_p, c_void_p, c_int, c_int, c_float, c_int, c_ulonglong, c_void_p, c_void_p, c_int,
-                          c_void_p],
+                          c_void_p, c_void_p],
         }
         for name, argtypes in sig.items():
             fn = getattr(lib, name)
@@ -107,6 +108,7 @@ class Ops:
         self.decode_copy = os.environ.get("STARTER_B200_DECODE_COPY", "auto")   # "1", "0" or "auto"
         self.use_stream = os.environ.get("STARTER_B200_STREAM", "1") != "0"  # the TMA + tcgen05 product for decode
         self._kernel_status = None
+        self._status_override = None
         self.decode_balanced = os.environ.get("STARTER_B200_ATTN", "balanced") != "split"
         self.fuse_qk = os.environ.get("STARTER_B200_FUSE_QK", "1") != "0"
         self.prefetch_next_bytes = int(os.environ.get("STARTER_B200_PREFETCH_MAX", 24 << 20))
@@ -227,9 +229,21 @@ class Ops:
 
     def kernel_status(self, device) -> torch.Tensor:
         """A status word of the kernels that are not tied to a step (bit 4: a wait inside a kernel timed out)."""
+        if self._status_override is not None:
+            return self._status_override
         if self._kernel_status is None:
             self._kernel_status = torch.zeros(1, dtype=torch.int32, device=device)
         return self._kernel_status
+
+    @contextlib.contextmanager
+    def status_into(self, word: torch.Tensor):
+        """While this is open, kernels that are not tied to a step raise their bits in ``word`` (int32 [1] on
+        the device): a captured step then carries all its status in the word that travels with its tokens."""
+        before, self._status_override = self._status_override, word
+        try:
+            yield
+        finally:
+            self._status_override = before
 
     def read_kernel_status(self) -> int:
         if self._kernel_status is None:
@@ -380,8 +394,8 @@ class Ops:
         256 blocks in all is best (more blocks mean shorter shares, and a share pays fixed costs: loading
         the queries, merging the warps, the pass through scratch memory), never more than 16 per pair.
         A function of shapes only, so that a captured graph stays valid as sequences grow."""
-        if os.environ.get("STARTER_B200_ATTN_SPLITS"):
-            return int(os.environ["STARTER_B200_ATTN_SPLITS"])
+        if os.environ.get("STARTER_B200_ATTN_SPLITS"):   # a tuning override; the kernel refuses what its merge cannot hold
+            return max(1, min(int(os.environ["STARTER_B200_ATTN_SPLITS"]), 256))
         pairs = max(n_seqs * n_kv_heads, 1)
         return max(1, min(256 // pairs, 16, max_pages, self.decode_resident(head_dim) // pairs))
 
@@ -510,11 +524,13 @@ class Ops:
                                        self._stream()), "argmax")
         return out
 
-    def sample(self, logits, temperature, top_k, seed, request_ids, steps, advance=False):
+    def sample(self, logits, temperature, top_k, seed, request_ids, steps, advance=False, device_params=None):
+        """``device_params``: int32 [4] on the device {temperature's float bits, top_k, seed low, seed high};
+        when given, the kernel reads them there as it runs (a captured step then serves every setting)."""
         out = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
         self._check(self.lib.sb_sample(_ptr(logits), _ptr(out), logits.shape[0], logits.shape[1], float(temperature),
                                        int(top_k), int(seed) & ((1 << 64) - 1), _ptr(request_ids), _ptr(steps),
-                                       int(bool(advance)), self._stream()), "sample")
+                                       int(bool(advance)), _ptr(device_params), self._stream()), "sample")
         return out
 
 

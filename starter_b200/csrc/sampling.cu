@@ -109,7 +109,8 @@ __device__ __forceinline__ V block_exclusive_scan(V v, V* warp_totals, V* total)
 // One block of SAMPLE_THREADS per row; thread t owns the indices [t*chunk, (t+1)*chunk).
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab, float temperature, int top_k,
-              unsigned long long seed, const int* __restrict__ request_ids, int* __restrict__ steps, int advance) {
+              unsigned long long seed, const int* __restrict__ request_ids, int* __restrict__ steps, int advance,
+              const unsigned int* __restrict__ device_params) {
     __shared__ unsigned int hist[256];
     __shared__ float red[33];
     __shared__ float fw[32];
@@ -120,6 +121,11 @@ sample_kernel(const float* __restrict__ logits, int* __restrict__ out, int vocab
     __shared__ int s_need;
     __shared__ int s_token;
     pdl_wait();
+    if (device_params) {  // a captured step reads what the host wrote for this batch, not what was captured
+        temperature = __uint_as_float(device_params[0]);
+        top_k = (int)device_params[1];
+        seed = (unsigned long long)device_params[2] | ((unsigned long long)device_params[3] << 32);
+    }
     const float* row = logits + (long long)blockIdx.x * vocab;
     const int tid = threadIdx.x;
     const int chunk = (vocab + SAMPLE_THREADS - 1) / SAMPLE_THREADS;
@@ -240,11 +246,14 @@ int sb_argmax(const float* logits, int* out, int rows, int vocab, float* scratch
 
 // request_ids [rows] and steps [rows] key the uniform number of each row; with advance != 0 the
 // kernel adds one to each row's step after use, so a replayed step draws a fresh number.
+// device_params (or null): four 32-bit words on the device {temperature's float bits, top_k, seed low,
+// seed high} that replace the three arguments of the same names when the kernel runs.
 int sb_sample(const float* logits, int* out, int rows, int vocab, float temperature, int top_k, unsigned long long seed,
-              const int* request_ids, int* steps, int advance, cudaStream_t stream) {
+              const int* request_ids, int* steps, int advance, const unsigned int* device_params, cudaStream_t stream) {
     if (rows <= 0) return 0;
-    if (!(temperature > 0.f)) return (int)cudaErrorInvalidValue;
-    sb_launch(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, out, vocab, temperature, top_k, seed, request_ids, steps, advance);
+    if (!device_params && !(temperature > 0.f)) return (int)cudaErrorInvalidValue;
+    sb_launch(sample_kernel, rows, SAMPLE_THREADS, 0, stream, logits, out, vocab, temperature, top_k, seed, request_ids, steps,
+              advance, device_params);
     SB_LAUNCH_CHECK();
 }
 

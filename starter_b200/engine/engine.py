@@ -39,6 +39,18 @@ class Engine:
                                max_seqs=max_batch, max_seq_tokens=max_context, device=device, ops=ops, verbose=verbose)
         self.generator = Generator(self.session, use_graphs=use_graphs)
 
+    @classmethod
+    def from_session(cls, session: Session, use_graphs: Optional[bool] = None) -> "Engine":
+        """The entry point around a model that is loaded already (a Session made from a folder or from
+        a configuration and a weight source)."""
+        if use_graphs is None:
+            use_graphs = os.environ.get("ENGINE_NO_GRAPHS") is None
+        engine = cls.__new__(cls)
+        engine.model_path = None
+        engine.session = session
+        engine.generator = Generator(session, use_graphs=use_graphs)
+        return engine
+
     @property
     def config(self):
         return self.session.config

@@ -67,7 +67,10 @@ class Generator:
 
     def __init__(self, session, use_graphs: bool = True):
         self.session = session
-        self.use_graphs = use_graphs and session.device.type == "cuda"
+        # a part that cannot run inside a captured graph (it reads device values on the host, say) sets
+        # ``capturable = False``; decoding then runs step by step
+        self.use_graphs = (use_graphs and session.device.type == "cuda"
+                           and all(getattr(part, "capturable", True) for part in session.model.parts()))
         self._decoders = {}
 
     def limits(self) -> BatchLimits:
@@ -121,9 +124,9 @@ class Generator:
                 if not live_next:
                     return
                 if self.use_graphs:
-                    decoder = self._decoder(len(live_next), sampling)
+                    decoder = self._decoder(sampling)
                     for step_tokens in decoder.run([slots[b] for b in live_next], feed, [ids[b] for b in live_next],
-                                                   produced, max_new_tokens - produced, stop):
+                                                   produced, max_new_tokens - produced, stop, sampling):
                         out = [None] * B
                         for b, t in zip(live_next, step_tokens):
                             out[b] = t
@@ -141,12 +144,13 @@ class Generator:
             for s in slots:
                 cache.free(s)
 
-    def _decoder(self, n_seqs: int, sampling: SamplingParams):
+    def _decoder(self, sampling: SamplingParams):
+        """One set of captured graphs for greedy runs, one for sampled runs: temperature, top-k and seed
+        are data that the sampling kernel reads on the device, so a new seed captures nothing."""
         from .graph import GraphDecoder
-        key = sampling
-        dec = self._decoders.get(key)
+        dec = self._decoders.get(sampling.greedy)
         if dec is None:
-            dec = self._decoders[key] = GraphDecoder(self.session, sampling)
+            dec = self._decoders[sampling.greedy] = GraphDecoder(self.session, sampling.greedy)
         return dec
 
     # ---- many requests -------------------------------------------------------------------

@@ -70,6 +70,16 @@ class DecoderModel:
         model.config = config
         return model
 
+    def parts(self):
+        """Every part object of the model: the final norm, each block, and what each block is made of."""
+        yield self.final_norm
+        for block, block_spec in zip(self.blocks, self.spec.layers):
+            yield block
+            for name, _, _ in type(block).sub_parts(block_spec):
+                part = getattr(block, name, None)
+                if part is not None:
+                    yield part
+
     # ---- cache -------------------------------------------------------------------------
 
     def cache_requests(self) -> List[object]:
@@ -98,7 +108,10 @@ class DecoderModel:
 
     def hidden(self, ctx: StepContext, tokens: torch.Tensor) -> ResidualStream:
         """Run the step's rows through every layer; returns the residual stream before the final norm."""
-        stream = ResidualStream(ctx.ops.embed(tokens, self.embedding, ctx.status))
+        x = ctx.ops.embed(tokens, self.embedding, ctx.status)
+        if self.spec.embedding_scale is not None:
+            x = (x.float() * self.spec.embedding_scale).to(x.dtype)
+        stream = ResidualStream(x)
         for pos, i in enumerate(self.order):
             self.blocks[i].forward(ctx, stream, ctx.cache.layers[pos])
         return stream
@@ -111,4 +124,9 @@ class DecoderModel:
             x = ops.gather_rows(x, rows)
             delta = ops.gather_rows(delta, rows) if delta is not None else None
         h = self.final_norm.add_forward(x, delta) if delta is not None else self.final_norm.forward(x)
-        return ops.linear(h, self.lm_head, out_float32=True)
+        logits = ops.linear(h, self.lm_head, out_float32=True)
+        if self.spec.logit_scale is not None:
+            logits = logits * self.spec.logit_scale
+        if self.spec.logit_softcap is not None:
+            logits = torch.tanh(logits / self.spec.logit_softcap) * self.spec.logit_softcap
+        return logits

@@ -49,8 +49,8 @@ class Session:
             from ..csrc.ops import get_ops
             if self.device.type != "cuda":
                 raise ValueError("the kernels of this library run on a CUDA device only")
+            ops = get_ops(verbose=verbose)   # first: without a CUDA device this raises the library's own error
             torch.cuda.set_device(self.device)
-            ops = get_ops(verbose=verbose)
         if dependent_launch is None:
             dependent_launch = os.environ.get("STARTER_B200_PDL", "1") != "0"
         if hasattr(ops, "set_dependent_launch"):

@@ -34,6 +34,13 @@ class StepError(RuntimeError):
     """A kernel of the step flagged bad input instead of reading or writing out of range."""
 
 
+def raise_status_bits(bits: int) -> None:
+    """Raise StepError for a status word with bits set."""
+    if bits:
+        what = [msg for bit, msg in STATUS_MESSAGES.items() if bits & bit] or [f"status {bits}"]
+        raise StepError("; ".join(what))
+
+
 @dataclass
 class StepEntry:
     """One sequence's share of a step: its slot, its next tokens, the places among them whose logits are wanted."""
@@ -167,6 +174,4 @@ class Stepper:
         read = getattr(self.runtime.ops, "read_kernel_status", None)
         if read is not None:
             bits |= read()
-        if bits:
-            what = [msg for bit, msg in STATUS_MESSAGES.items() if bits & bit] or [f"status {bits}"]
-            raise StepError("; ".join(what))
+        raise_status_bits(bits)

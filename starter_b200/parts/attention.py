@@ -11,6 +11,12 @@ query head h reading key/value head h // (heads / kv_heads)
 Sizes, scale, window, the norm's eps and the position encoding all come from
 the spec.  A layer with ``kv_from`` projects queries only and reads the
 cache of the layer it names.
+
+The position part is either rotary (it offers ``fused_rotary()``: norm,
+rotation and the cache write then run in one kernel) or anything with
+``apply(ctx, q, k) -> (q, k)`` over the normed heads (q [rows, heads, D], k
+[rows, kv_heads, D], or None for a layer that stores none): the steps then
+run one after another.  A layer without a position part rotates nothing.
 """
 
 from __future__ import annotations
@@ -55,8 +61,9 @@ class Attention:
         self.q_norm = weights.get("q_norm")
         self.k_norm = weights.get("k_norm")
         self.position = build_part("position", spec.position, {}, runtime) if spec.position is not None else None
-        if self.position is not None and not hasattr(self.position, "fused_rotary"):
-            raise ValueError("the attention part needs a position part that offers fused_rotary()")
+        self.fused_position = self.position is None or hasattr(self.position, "fused_rotary")
+        if not self.fused_position and not hasattr(self.position, "apply"):
+            raise ValueError("a position part offers fused_rotary() or apply(ctx, q, k)")
 
     def cache_request(self):
         if not self.stores_kv:
@@ -67,8 +74,30 @@ class Attention:
         if self.position is not None:
             self.position.prepare(cache.max_seq_tokens)
 
+    def _positions_applied(self, ctx, qkv):
+        """q/k/v rows with the per-head norm taken and the position part's ``apply`` run over q and k."""
+        rows, d, hq = qkv.shape[0], self.head_dim, self.num_heads
+        hkv = self.num_kv_heads if self.stores_kv else 0
+        q = qkv[:, :hq * d].reshape(rows * hq, d).contiguous()
+        k = qkv[:, hq * d:(hq + hkv) * d].reshape(rows * hkv, d).contiguous() if hkv else None
+        if self.q_norm is not None:
+            q = self.ops.rmsnorm(q, self.q_norm, self.norm_eps)
+        if k is not None and self.k_norm is not None:
+            k = self.ops.rmsnorm(k, self.k_norm, self.norm_eps)
+        q, k = self.position.apply(ctx, q.view(rows, hq, d), k.view(rows, hkv, d) if k is not None else None)
+        pieces = [q.reshape(rows, hq * d)]
+        if hkv:
+            pieces += [k.reshape(rows, hkv * d), qkv[:, (hq + hkv) * d:]]
+        return torch.cat(pieces, dim=1).contiguous()
+
     def forward(self, ctx, h, layer_cache):
         qkv = self.ops.linear(h, self.w_qkv)
+        if not self.fused_position:
+            n_kv = self.num_kv_heads if self.stores_kv else 0
+            q = self.ops.qk_norm_rope_store(ctx, self._positions_applied(ctx, qkv), layer_cache, self.num_heads, n_kv,
+                                            self.head_dim, None, None, 0.0, None)
+            a = self.ops.attention(ctx, q, layer_cache, self.num_heads, self.scale, self.window)
+            return self.ops.linear(a, self.w_o)
         rotary = self.position.fused_rotary() if self.position is not None else None
         n_kv = self.num_kv_heads if self.stores_kv else 0
         a = None

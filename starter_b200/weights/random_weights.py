@@ -50,16 +50,19 @@ class RandomSource:
         return (MATRIX_STD * noise).to(self.dtype)
 
 
-def write_model_folder(config, seed: int, folder, dtype: torch.dtype = torch.bfloat16, shards: int = 1) -> Path:
+def write_model_folder(config, seed: int, folder, dtype: torch.dtype = torch.bfloat16, shards: int = 1,
+                       device="cpu") -> Path:
     """Write ``config.json`` and ``model.safetensors`` for ``config`` with seeded random weights.
 
     ``shards`` > 1 writes ``model-0000i-of-0000n.safetensors`` files instead, the
     tensors dealt out in order in runs of about equal bytes, the way published
-    checkpoints are laid out (no index file: the loader needs none).
+    checkpoints are laid out (no index file: the loader needs none).  ``device``
+    is where the numbers are drawn (a GPU draws a large model in seconds; its
+    generator gives other values than the CPU's for the same seed).
     """
     folder = Path(folder)
     save_config(config, folder)
-    source = RandomSource(config, seed, dtype=dtype)
+    source = RandomSource(config, seed, dtype=dtype, device=device)
     items = list(source.entries.items())
     if shards <= 1:
         write_safetensors(folder / "model.safetensors", items, source.get)

@@ -55,10 +55,30 @@ def tiny_raw(name: str) -> dict:
     return raw
 
 
+class TinyFolders(dict):
+    """name -> folder with config.json and model.safetensors in bfloat16.  ``for_dtype(name, "float32")``
+    is a folder of the same configuration whose weights are stored in 32-bit and are not bfloat16
+    numbers, split over three shard files: a 32-bit run that rounded a weight through bfloat16
+    anywhere could not match the plain implementation on it."""
+
+    def __init__(self, factory):
+        super().__init__()
+        self._factory = factory
+        self._wide = {}
+
+    def for_dtype(self, name: str, dtype: str):
+        if dtype != "float32":
+            return self[name]
+        if name not in self._wide:
+            folder = self._factory.mktemp(f"tiny_{name}_f32")
+            write_model_folder(config_from_dict(tiny_raw(name)), TINY[name]["seed"], folder, dtype=torch.float32, shards=3)
+            self._wide[name] = folder
+        return self._wide[name]
+
+
 @pytest.fixture(scope="session")
 def tiny_folders(tmp_path_factory):
-    """name -> folder with config.json and model.safetensors (bfloat16 weights)."""
-    out = {}
+    out = TinyFolders(tmp_path_factory)
     for name in TINY:
         folder = tmp_path_factory.mktemp(f"tiny_{name}")
         write_model_folder(config_from_dict(tiny_raw(name)), TINY[name]["seed"], folder)

@@ -146,8 +146,13 @@ class EmulatedOps:
     def argmax(self, logits):
         return logits.float().argmax(dim=-1).to(torch.int32)
 
-    def sample(self, logits, temperature, top_k, seed, request_ids, steps, advance=False):
+    def sample(self, logits, temperature, top_k, seed, request_ids, steps, advance=False, device_params=None):
         from plain import qwen3_plain as plain
+        if device_params is not None:
+            import struct
+            words = [int(v) & 0xffffffff for v in device_params.tolist()]
+            (temperature,) = struct.unpack("<f", struct.pack("<I", words[0]))
+            top_k, seed = words[1], words[2] | (words[3] << 32)
         out = []
         for r in range(logits.shape[0]):
             req = int(request_ids[r]) if request_ids is not None else r

@@ -13,7 +13,7 @@ LENGTHS = (5, 150, 77, 1, 64, 65)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", list(TINY))
 def test_every_cutting_matches_plain(tiny_folders, name, dtype):
-    folder = tiny_folders[name]
+    folder = tiny_folders.for_dtype(name, dtype)
     seqs = random_tokens(TINY[name]["vocab_size"], LENGTHS, seed=11)
     ref = plain_logits(folder, seqs, dtype)
     # max_step_tokens below the longest request: its prompt runs as several forward passes

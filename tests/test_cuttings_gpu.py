@@ -13,7 +13,7 @@ LENGTHS = (5, 150, 77, 1, 64, 65, 33)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", list(TINY))
 def test_every_cutting_matches_plain(tiny_folders, name, dtype):
-    folder = tiny_folders[name]
+    folder = tiny_folders.for_dtype(name, dtype)
     seqs = random_tokens(TINY[name]["vocab_size"], LENGTHS, seed=11)
     ref = plain_logits(folder, seqs, dtype)
     sess = make_session(folder, dtype, max_tokens=64 * 10, max_seqs=4, max_step_tokens=48, max_rows=100)
@@ -28,7 +28,7 @@ def test_every_cutting_matches_plain(tiny_folders, name, dtype):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_first_tokens_of_a_sequence(tiny_folders, dtype):
     """Sequences of one, two and three tokens, alone and in one step: position 0 has a single key."""
-    folder = tiny_folders["B"]
+    folder = tiny_folders.for_dtype("B", dtype)
     seqs = random_tokens(TINY["B"]["vocab_size"], (1, 2, 3, 1), seed=13)
     ref = plain_logits(folder, seqs, dtype)
     sess = make_session(folder, dtype, max_tokens=64 * 4, max_seqs=4)

@@ -7,6 +7,7 @@ import torch
 from conftest import TINY, random_tokens
 from plain import qwen3_plain as plain
 from starter_b200.engine import Engine
+from starter_b200.sampling import SamplingParams
 
 pytestmark = pytest.mark.gpu
 
@@ -109,3 +110,76 @@ def test_greedy_on_the_tensor_core_kernels(tiny_folders, name, graphs):
     again = list(eng.generate(prompts[:2], 10))                             # fewer requests, slots used again
     assert [[s[b] for s in again] for b in range(2)] == got[:2]
     assert eng.session.cache.slots.n_held == 0
+
+
+def test_ended_sequences_leave_the_captured_batch(tiny_folders):
+    """Under graphs a sequence that meets a stop token stops being computed: the loop drains the steps in
+    flight and goes on with the graph of a smaller batch, and the survivors' tokens do not change."""
+    prompts = random_tokens(256, (5, 9, 12, 30, 2, 17, 40, 3), seed=5)
+    eng = Engine(tiny_folders["A"], dtype="float32", max_batch=8, max_context=128, use_graphs=True)
+    free_run = eng.generate_all(prompts, 24)
+    decoder = eng.generator._decoder(SamplingParams())
+    assert decoder.history == [[8, 23]]                      # one graph of 8 rows for all 23 decode steps
+    # stop tokens that end six of the eight sequences early, at different steps
+    stop = {free_run[b][3 + b] for b in range(6)}
+    got = eng.generate_all(prompts, 24, stop_token_ids=stop)
+    for b, (g, full) in enumerate(zip(got, free_run)):
+        cut = next((i for i, t in enumerate(full) if t in stop), len(full) - 1)
+        assert g == full[:cut + 1], f"request {b}"
+    sizes = [size for size, _ in decoder.history]
+    assert sizes[0] == 8 and sizes == sorted(sizes, reverse=True) and sizes[-1] <= 2, decoder.history
+    assert sum(steps for _, steps in decoder.history) <= 23 + 3 * (len(sizes) - 1)   # at most the steps in flight are redone
+    eager = Engine(tiny_folders["A"], dtype="float32", max_batch=8, max_context=128, use_graphs=False)
+    assert eager.generate_all(prompts, 24, stop_token_ids=stop) == got
+    assert eng.session.cache.slots.n_held == 0
+    eng.session.cache.check()
+
+
+def test_a_new_seed_replays_the_same_graphs(tiny_folders):
+    """Temperature, top-k and seed are data on the device: runs that differ in them share one set of captured graphs,
+    and each gives the tokens of the step-by-step loop with the same settings."""
+    prompts = random_tokens(389, (1, 7, 16), seed=6)
+    eng = Engine(tiny_folders["B"], dtype="float32", max_batch=4, max_context=128, use_graphs=True)
+    eager = Engine(tiny_folders["B"], dtype="float32", max_batch=4, max_context=128, use_graphs=False)
+    outs = []
+    for temperature, top_k, seed in [(0.8, 0, 1), (0.8, 0, 2), (1.3, 5, 2 ** 40 + 7), (0.8, 0, 1)]:
+        outs.append(eng.generate_all(prompts, 10, temperature=temperature, top_k=top_k, seed=seed))
+        assert outs[-1] == eager.generate_all(prompts, 10, temperature=temperature, top_k=top_k, seed=seed)
+    assert outs[0] == outs[3] and outs[0] != outs[1]
+    assert set(eng.generator._decoders) == {False}           # one decoder for every sampled run
+    assert list(eng.generator._decoders[False].buckets) == [4]
+    eng.generate_all(prompts, 4)
+    assert set(eng.generator._decoders) == {False, True}
+
+
+def test_a_bad_token_raises_through_the_entry_point(tiny_folders):
+    """A token id outside the vocabulary sets a status bit in the kernel instead of reading out of range; the
+    loop raises it as StepError, with graphs and without, and the engine serves the next call."""
+    from starter_b200.engine.step import StepError
+    for graphs in (False, True):
+        eng = Engine(tiny_folders["A"], dtype="float32", max_batch=2, max_context=64, use_graphs=graphs)
+        with pytest.raises(StepError, match="outside the vocabulary"):
+            eng.generate_all([[1, 2, 300]], 4)
+        assert eng.session.cache.slots.n_held == 0
+        assert len(eng.generate_all([[1, 2, 3]], 4)[0]) == 4
+
+
+def test_a_captured_step_brings_its_status_with_its_tokens(tiny_folders):
+    """Fed a token id outside the vocabulary, a replayed step raises its status bit in the word that is copied
+    to the host with the step's tokens: the error comes before those tokens are handed out."""
+    from starter_b200.engine.graph import GraphDecoder
+    from starter_b200.engine.session import Session
+    from starter_b200.engine.step import StepEntry, StepError
+    sess = Session(tiny_folders["A"], dtype="float32", max_tokens=256, max_seqs=2, verbose=False)
+    slot = sess.cache.alloc()
+    sess.stepper.step([StepEntry(slot, [1, 2, 3], [])])
+    sess.cache.reserve(slot, 16)
+    decoder = GraphDecoder(sess, SamplingParams())
+    with pytest.raises(StepError, match="outside the vocabulary"):
+        list(decoder.run([slot], [256], [0], 1, 4))
+    sess.cache.free(slot)
+    slot = sess.cache.alloc()                                  # the same graph serves the next batch
+    sess.stepper.step([StepEntry(slot, [1, 2, 3], [])])
+    sess.cache.reserve(slot, 16)
+    assert len(list(decoder.run([slot], [7], [0], 1, 4))) == 4
+    sess.cache.free(slot)

@@ -46,6 +46,8 @@ class DecayMixer:
     def prepare(self, cache):
         pass
 
+    capturable = False   # forward reads device values on the host: decoding must run step by step
+
     def forward(self, ctx, h, layer_cache):
         u = self.ops.linear(h, self.w_in).float()
         cu, slots = ctx.cu_q.tolist(), ctx.seq_slot.tolist()
@@ -62,21 +64,42 @@ class DecayMixer:
 register_part("mixer", "toy_decay", DecayMixer)
 
 
+class GraphDecayMixer(DecayMixer):
+    """The same mixer with its one-token step written in tensor operations only (state records gathered and
+    scattered by the step's slot vector), so that a decode step with it can be captured and replayed."""
+
+    capturable = True
+
+    def forward(self, ctx, h, layer_cache):
+        if not ctx.is_decode:
+            return super().forward(ctx, h, layer_cache)
+        u = self.ops.linear(h, self.w_in).float()
+        slots = ctx.seq_slot.long()                      # padding rows name the null slot's record
+        s = self.spec.decay * layer_cache.state[slots] + u
+        layer_cache.state.index_copy_(0, slots, s)
+        return self.ops.linear(s.to(h.dtype), self.w_out)
+
+
+register_part("mixer", "toy_decay_graph", GraphDecayMixer)
+
+
 @dataclass(frozen=True)
 class ToyConfig(ModelConfig):
     hidden: int
     state: int
     vocab: int
     decay: float
+    mixer_kind: str = "toy_decay"
     architecture = "ToyDecayForCausalLM"
 
     @classmethod
     def from_dict(cls, raw):
-        return cls(hidden=raw["hidden"], state=raw["state"], vocab=raw["vocab"], decay=raw["decay"])
+        return cls(hidden=raw["hidden"], state=raw["state"], vocab=raw["vocab"], decay=raw["decay"],
+                   mixer_kind=raw.get("mixer_kind", "toy_decay"))
 
     def to_dict(self):
         return {"architectures": [self.architecture], "hidden": self.hidden, "state": self.state, "vocab": self.vocab,
-                "decay": self.decay}
+                "decay": self.decay, "mixer_kind": self.mixer_kind}
 
     def model_spec(self):
         norm = NormSpec(size=self.hidden, eps=1e-5)
@@ -84,7 +107,8 @@ class ToyConfig(ModelConfig):
         att = dict(hidden_size=self.hidden, num_heads=4, num_kv_heads=2, head_dim=16, scale=0.25,
                    position=RopeSpec(theta=10000.0, rotary_dim=16))
         layers = (
-            BlockSpec(mixer_norm=norm, mixer=DecaySpec(self.hidden, self.state, self.decay), ff_norm=norm, ff=ff),
+            BlockSpec(mixer_norm=norm, mixer=DecaySpec(self.hidden, self.state, self.decay, self.mixer_kind),
+                      ff_norm=norm, ff=ff),
             BlockSpec(mixer_norm=norm, mixer=AttentionSpec(**att), ff_norm=norm, ff=ff),
             BlockSpec(mixer_norm=norm, mixer=AttentionSpec(kv_from=1, **att), ff_norm=norm, ff=ff),
         )
@@ -145,3 +169,26 @@ def test_toy_model_generates_through_the_entry_point(toy_folder):
     assert [len(o) for o in outs] == [6, 6, 6]
     solo = Engine(toy_folder, dtype="float32", max_batch=1, max_context=64, use_graphs=False)
     assert solo.generate_all([[1, 2, 3], [4, 5, 6, 7, 8], [9]], 6) == outs
+
+
+def test_state_mixer_under_captured_graphs(toy_folder, tmp_path):
+    """A mixer that says it cannot be captured makes the loop decode step by step; one written in tensor
+    operations decodes through replayed graphs, its state records updated inside them, and gives the same
+    tokens as the step-by-step loop, for prompts of unequal length and a sequence that stops early."""
+    prompts = [[1, 2, 3], [4, 5, 6, 7, 8], [9]]
+    plain_loop = Engine(toy_folder, dtype="float32", max_batch=4, max_context=64, use_graphs=True)
+    assert plain_loop.generator.use_graphs is False
+    want = plain_loop.generate_all(prompts, 12)
+    cfg = config_from_dict({"architectures": ["ToyDecayForCausalLM"], "hidden": 48, "state": 24, "vocab": 97, "decay": 0.9,
+                            "mixer_kind": "toy_decay_graph"})
+    write_model_folder(cfg, 3, tmp_path)                       # same seed and tensor names: the same weights
+    eng = Engine(tmp_path, dtype="float32", max_batch=4, max_context=64, use_graphs=True)
+    assert eng.generator.use_graphs is True
+    assert eng.generate_all(prompts, 12) == want
+    assert eng.generate_all(prompts, 12) == want              # state records were reset when the slots were taken again
+    stop = {want[1][4]}
+    stopped = eng.generate_all(prompts, 12, stop_token_ids=stop)
+    for got, full in zip(stopped, want):
+        cut = next((i for i, t in enumerate(full) if t in stop), len(full) - 1)
+        assert got == full[:cut + 1]
+    eng.session.cache.check()

@@ -33,7 +33,7 @@ def read(out_dir, step, vocab):
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", ["B", "W"])
 def test_replay_in_three_cuttings(tiny_folders, tmp_path, name, dtype):
-    folder, vocab = tiny_folders[name], TINY[name]["vocab_size"]
+    folder, vocab = tiny_folders.for_dtype(name, dtype), TINY[name]["vocab_size"]   # float32: 32-bit weights in three shards
     seqs = random_tokens(vocab, (40, 130, 7, 64), seed=21)
     ref = plain_logits(folder, seqs, dtype)
     scale = max(float(r.abs().max()) for r in ref)
