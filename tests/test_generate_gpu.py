@@ -115,22 +115,25 @@ def test_greedy_on_the_tensor_core_kernels(tiny_folders, name, graphs):
 def test_ended_sequences_leave_the_captured_batch(tiny_folders):
     """Under graphs a sequence that meets a stop token stops being computed: the loop drains the steps in
     flight and goes on with the graph of a smaller batch, and the survivors' tokens do not change."""
-    prompts = random_tokens(256, (5, 9, 12, 30, 2, 17, 40, 3), seed=5)
-    eng = Engine(tiny_folders["A"], dtype="float32", max_batch=8, max_context=128, use_graphs=True)
-    free_run = eng.generate_all(prompts, 24)
-    decoder = eng.generator._decoder(SamplingParams())
+    prompts = random_tokens(389, (5, 9, 12, 30, 2, 17, 40, 3), seed=5)
+    eng = Engine(tiny_folders["B"], dtype="float32", max_batch=8, max_context=128, use_graphs=True)
+    free_run = eng.generate_all(prompts, 24, temperature=1.0, seed=11)       # sampled: the sequences do not repeat themselves
+    decoder = eng.generator._decoder(SamplingParams(temperature=1.0))
     assert decoder.history == [[8, 23]]                      # one graph of 8 rows for all 23 decode steps
-    # stop tokens that end six of the eight sequences early, at different steps
-    stop = {free_run[b][3 + b] for b in range(6)}
-    got = eng.generate_all(prompts, 24, stop_token_ids=stop)
+    # stop tokens that end six of the eight sequences early, at different steps, none of them within the first three
+    early = {t for seq in free_run for t in seq[:3]}
+    stop = set()
+    for b in range(6):
+        stop.add(next(t for t in free_run[b][3 + 2 * b:] if t not in early))
+    got = eng.generate_all(prompts, 24, stop_token_ids=stop, temperature=1.0, seed=11)
     for b, (g, full) in enumerate(zip(got, free_run)):
         cut = next((i for i, t in enumerate(full) if t in stop), len(full) - 1)
         assert g == full[:cut + 1], f"request {b}"
     sizes = [size for size, _ in decoder.history]
     assert sizes[0] == 8 and sizes == sorted(sizes, reverse=True) and sizes[-1] <= 2, decoder.history
     assert sum(steps for _, steps in decoder.history) <= 23 + 3 * (len(sizes) - 1)   # at most the steps in flight are redone
-    eager = Engine(tiny_folders["A"], dtype="float32", max_batch=8, max_context=128, use_graphs=False)
-    assert eager.generate_all(prompts, 24, stop_token_ids=stop) == got
+    eager = Engine(tiny_folders["B"], dtype="float32", max_batch=8, max_context=128, use_graphs=False)
+    assert eager.generate_all(prompts, 24, stop_token_ids=stop, temperature=1.0, seed=11) == got
     assert eng.session.cache.slots.n_held == 0
     eng.session.cache.check()
 
