@@ -69,4 +69,6 @@ def main(reference: str) -> None:
 
 
 if __name__ == "__main__":
-    main(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) != 2:
+        sys.exit("usage: make_golden.py /path/to/reference   (the folder that holds engine/)")
+    main(sys.argv[1])
