@@ -33,7 +33,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
     unsigned char* kv_s = smem + AP_ROWS * D * 2;  // [2 stages][K tile | V tile]
     pdl_wait();
 
-    const int seq = blockIdx.z, kvh = blockIdx.y;
+    const int seq = blockIdx.z, kvh = blockIdx.x;   // kv head fastest: blocks start longest first across all heads
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int G = n_heads / kv.n_kv_heads;
     const int slot = batch.seq_slot[seq];
@@ -41,7 +41,7 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restri
     const int q_len = batch.cu_q[seq + 1] - row0;
     const int start = batch.lengths[slot];                      // position of the sequence's first new row
     const int total = q_len * G;                                // (position, head) rows of this sequence and kv head
-    const int tile = gridDim.x - 1 - blockIdx.x;                // latest rows (most keys) first
+    const int tile = gridDim.y - 1 - blockIdx.y;                // latest rows (most keys) first
     const int t0 = tile * AP_ROWS;
     if (t0 >= total) return;
     const int t_last = min(t0 + AP_ROWS, total) - 1;
@@ -238,8 +238,8 @@ template <int D> static int launch_prefill(const void* q, void* out, SbBatch bat
     }
     const int G = n_heads / kv.n_kv_heads;
     const long long tiles = ((long long)max_q_len * G + AP_ROWS - 1) / AP_ROWS;
-    if (tiles > 2147483647LL || kv.n_kv_heads > 65535 || batch.n_seqs > 65535) return (int)cudaErrorInvalidValue;
-    dim3 grid((unsigned int)tiles, kv.n_kv_heads, batch.n_seqs);
+    if (tiles > 65535 || batch.n_seqs > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid(kv.n_kv_heads, (unsigned int)tiles, batch.n_seqs);
     sb_launch(attn_prefill_kernel<D>, grid, AP_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv,
                                                                   n_heads, scale * 1.4426950408889634f, window);
     return (int)cudaGetLastError();

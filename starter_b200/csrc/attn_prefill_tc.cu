@@ -10,9 +10,9 @@
 // thread and per lane of tensor memory.  Per key page (64 keys, one cache page):
 //   thread 0 issues  S[128 x 64] = Q[128 x 128] K^T          (8 tcgen05.mma of K = 16, both operands K-major)
 //   every thread reads its row of S from tensor memory, masks, updates its running maximum and sum,
-//   and writes its row of P (bfloat16) into shared memory in the layout the tensor core reads
-//   thread 0 issues  O_page[128 x 128] = P[128 x 64] V       (4 tcgen05.mma; V as it lies in the cache,
-//                                                             [key][d], is the MN-major form of that operand)
+//   and writes its row of P (bfloat16) back into tensor memory, over the first half of the S it read
+//   thread 0 issues  O_page[128 x 128] = P[128 x 64] V       (4 tcgen05.mma with P read from tensor memory; V as
+//                                                             it lies in the cache, [key][d], is the MN-major form)
 //   every thread reads its row of O_page and folds it into its 128 accumulators: acc = acc * alpha + O_page.
 // Who does what.  Warps 0-3 own the rows (softmax).  One thread of a fifth warp issues every TMA copy and every
 // tcgen05.mma and nothing else: issuing a product takes about as long as the tensor core needs for it (measured:
@@ -21,7 +21,7 @@
 // while the rows work on page i, and O += P V of page i runs while they start on page i + 1.  Keys arrive two
 // pages ahead and values one page ahead, in two stages each.  The rows and the issuer meet only through
 // mbarriers (S ready, O done, P written); there is no block-wide barrier inside the loop.  Two blocks share an SM
-// (113 KB of shared memory and 256 columns of tensor memory each).  Every wait on an mbarrier is bounded; on a time-out the block raises
+// (97 KB of shared memory and 256 columns of tensor memory each).  Every wait on an mbarrier is bounded; on a time-out the block raises
 // SB_STATUS_TIMEOUT and a flag in shared memory that ends every other wait of the block, which then frees its
 // tensor memory and returns.
 #include <cuda.h>
@@ -47,8 +47,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     unsigned char* q_s = smem;                     // 2 blocks of [128][64]
     unsigned char* k_s = q_s + 2 * Q_ATOM;         // [2 stages][2 blocks of [64][64]]
     unsigned char* v_s = k_s + 2 * STAGE;          // [2 stages][2 blocks of [64][64]]
-    unsigned char* p_s = v_s + 2 * STAGE;          // [128][64] probabilities
-    uint64_t* bars = (uint64_t*)(p_s + PT_ROWS * 128);
+    uint64_t* bars = (uint64_t*)(v_s + 2 * STAGE);
     uint64_t* k_full = bars;                       // [2] keys of a page have landed in stage i & 1
     uint64_t* v_full = bars + 2;                   // [2] values likewise
     uint64_t* s_done = bars + 4;                   // [2] S of page i is in S buffer i & 1 (and every product issued before it is done)
@@ -63,7 +62,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         return;
     }
 
-    const int seq = blockIdx.z, kvh = blockIdx.y;
+    const int seq = blockIdx.z, kvh = blockIdx.x;
     const int tid = threadIdx.x, warp = tid >> 5;
     const int G = n_heads / kv.n_kv_heads;
     const int slot = batch.seq_slot[seq];
@@ -71,7 +70,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int q_len = batch.cu_q[seq + 1] - row0;
     const int start = batch.lengths[slot];
     const int total = q_len * G;
-    const int tile = gridDim.x - 1 - blockIdx.x;   // latest rows (most keys) first
+    // Blocks start in the order of their index, x fastest: with the kv head in x and the row tile in y, the blocks of a
+    // sequence start longest first across all heads (latest rows = most keys), and the short ones fill the gaps at the
+    // end.  With the tile in x the long blocks of the last heads started late: 78 against 58 us at 2,048 tokens.
+    const int tile = gridDim.y - 1 - blockIdx.y;
     const int t0 = tile * PT_ROWS;
     if (t0 >= total) return;
     const int t_last = min(t0 + PT_ROWS, total) - 1;
@@ -170,8 +172,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 const unsigned char* vt = v_s + b * STAGE;
 #pragma unroll
                 for (int ks = 0; ks < SB_PAGE / 16; ++ks)   // 16 keys per step: 32 bytes along P's rows, two groups of eight key rows of V
-                    tc_mma(tmem + O_COL, desc_k_major(p_s) + 2 * ks, desc_mn_major(vt + ks * 2048, KV_ATOM), idesc_o,
-                           (i > 0 || ks > 0) ? 1u : 0u);
+                    tc_mma_ts(tmem + O_COL, tmem + b * SB_PAGE + 8 * ks, desc_mn_major(vt + ks * 2048, KV_ATOM), idesc_o,
+                              (i > 0 || ks > 0) ? 1u : 0u);
                 tc_commit(&o_done[b]);
                 if (i + 1 < n_pages) {   // values of the next page go into the stage of page i - 1, once its product is done
                     if (i > 0) mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, status);
@@ -240,15 +242,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
             l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
 
-            // O += P V of the page before must be done before P is overwritten or the accumulator rescaled.  It was
-            // issued before this iteration began, so this wait is over by the time the arithmetic above is.
-            if (i > 0) {
+            // The accumulator of earlier pages moves to the new reference (rare after the first pages): O += P V of
+            // the page before must be done before it is rescaled.
+            if (i > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
                 mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, status);
                 if (*abort_flag) break;
                 tc_fence_after();
-            }
-            // the accumulator of earlier pages moves to the new reference (rare after the first pages)
-            if (i > 0 && __any_sync(0xffffffffu, alpha != 1.0f)) {
 #pragma unroll
                 for (int d0 = 0; d0 < PT_D; d0 += 32) {
                     float o[32];
@@ -270,12 +269,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
 #pragma unroll
                     for (int c = 0; c < 16; ++c)   // [2 blocks of 64 columns][64 keys][128 bytes]: the whole row, whatever the swizzle
                         *reinterpret_cast<uint4*>(vt + (c >> 3) * KV_ATOM + tid * 128 + ((c & 7) << 4)) = make_uint4(0u, 0u, 0u, 0u);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // ordinary stores, read by the tensor core
                 }
             }
-#pragma unroll
-            for (int c = 0; c < SB_PAGE / 8; ++c)
-                *reinterpret_cast<uint4*>(p_s + tid * 128 + (((c ^ (tid & 7))) << 4)) = packed[c];
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // P was written by ordinary stores
+            // P goes where this row's S was: 64 bfloat16 = 32 columns of the S buffer, which the product reads as its
+            // operand A straight from tensor memory.  (The tensor core runs a block's products in the order they were
+            // issued: S of page i + 2, which overwrites this buffer, is issued after O += P V of page i.)
+            tc_st32_u32(tmem_row + b * SB_PAGE, reinterpret_cast<const uint32_t*>(packed));
             tc_fence_before();
             mbar_arrive(p_ready);
         }
@@ -348,7 +348,7 @@ extern "C" int sb_attn_prefill_tc(const void* q, void* out, SbBatch batch, SbKV 
                                   int max_q_len, int n_pages, int* status, cudaStream_t stream) {
     if (batch.n_rows <= 0) return 0;
     if (kv.head_dim != PT_D || n_heads % kv.n_kv_heads || max_q_len < 1 || n_pages < 1) return (int)cudaErrorInvalidValue;
-    const int smem = 2 * PT_ROWS * 128 + 4 * 2 * SB_PAGE * 128 + PT_ROWS * 128 + 96 + PT_IDS * 4;
+    const int smem = 2 * PT_ROWS * 128 + 4 * 2 * SB_PAGE * 128 + 96 + PT_IDS * 4;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -363,8 +363,8 @@ extern "C" int sb_attn_prefill_tc(const void* q, void* out, SbBatch batch, SbKV 
     if (e) return e;
     const int G = n_heads / kv.n_kv_heads;
     const long long tiles = ((long long)max_q_len * G + PT_ROWS - 1) / PT_ROWS;
-    if (tiles > 2147483647LL || kv.n_kv_heads > 65535 || batch.n_seqs > 65535) return (int)cudaErrorInvalidValue;
-    dim3 grid((unsigned int)tiles, kv.n_kv_heads, batch.n_seqs);
+    if (tiles > 65535 || batch.n_seqs > 65535) return (int)cudaErrorInvalidValue;
+    dim3 grid(kv.n_kv_heads, (unsigned int)tiles, batch.n_seqs);
     sb_launch(attn_prefill_tc_kernel, grid, PT_THREADS, smem, stream, mk, mv, (const __nv_bfloat16*)q, (__nv_bfloat16*)out, batch, kv, n_heads,
               scale * 1.4426950408889634f, window, status);
     return (int)cudaGetLastError();
