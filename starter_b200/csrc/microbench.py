@@ -5,6 +5,7 @@ kernels the same way (engine/kernels/gemm.py:477-513).
     python -m starter_b200.csrc.microbench --kernel stream --shape gateup --rows 8
     python -m starter_b200.csrc.microbench --kernel attn_decode --rows 8 --context 4096
     python -m starter_b200.csrc.microbench --kernel attn_prefill --tokens 2048 --context 2048
+    python -m starter_b200.csrc.microbench --kernel rope_store --rows 2048      (also rmsnorm, swiglu)
 """
 
 from __future__ import annotations
@@ -116,9 +117,46 @@ def bench_attn_prefill(ops, tokens: int, context: int, heads: int, kv_heads: int
     return {"kernel": "attn_prefill", "tokens": tokens, "context": context, "us": round(us, 2), "TFLOP/s": round(flops / us / 1e6, 1)}
 
 
+def bench_rows(ops, kernel: str, rows: int, copies: int = 6):
+    """The row-wise kernels of a prefill at the 4B layer sizes: add + norm, q/k norm + rotary + cache store, SwiGLU."""
+    from ..cache import Cache, KVRequest
+    from ..engine.context import Runtime, StepContext
+    dt = torch.bfloat16
+    H, I, HQ, HKV, D = 2560, 9728, 32, 8, 128
+    if kernel == "rmsnorm":
+        xs = [torch.randn(rows, H, device="cuda", dtype=dt) for _ in range(copies)]
+        d = torch.randn(rows, H, device="cuda", dtype=dt)
+        w = torch.ones(H, device="cuda", dtype=dt)
+        calls = [lambda x=x: ops.add_rmsnorm(x, d, w, 1e-6) for x in xs]
+        nbytes = 4 * rows * H * 2
+    elif kernel == "swiglu":
+        gus = [torch.randn(rows, 2 * I, device="cuda", dtype=dt) for _ in range(copies)]
+        calls = [lambda g=g: ops.swiglu(g) for g in gus]
+        nbytes = 3 * rows * I * 2
+    else:
+        cache = Cache([KVRequest(HKV, D)] * copies, n_slots=1, max_tokens=rows, dtype=dt, device="cuda", max_seq_tokens=rows,
+                      max_step_tokens=rows)
+        slot = cache.alloc()
+        cache.reserve(slot, rows)
+        cache.flush()
+        i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
+        ctx = StepContext(runtime=Runtime(dt, torch.device("cuda"), ops), cache=cache, n_seqs=1, n_rows=rows, max_q_len=rows,
+                          kv_bound=rows, seq_slot=i32([slot]), cu_q=i32([0, rows]), row_seq=i32([0] * rows), lengths=cache.lengths,
+                          status=torch.zeros(1, dtype=torch.int32, device="cuda"))
+        qkvs = [torch.randn(rows, (HQ + 2 * HKV) * D, device="cuda", dtype=dt) for _ in range(copies)]
+        qn = torch.ones(D, device="cuda", dtype=dt)
+        ang = torch.arange(rows, dtype=torch.float32)[:, None] / (5e6 ** (torch.arange(D // 2).float() / (D // 2)))[None]
+        rotary = (ang.cos().to(dt).cuda(), ang.sin().to(dt).cuda(), D)
+        calls = [lambda q=q, lc=lc: ops.qk_norm_rope_store(ctx, q, lc, HQ, HKV, D, qn, qn, 1e-6, rotary)
+                 for q, lc in zip(qkvs, cache.layers)]
+        nbytes = rows * ((HQ + 2 * HKV) + HQ + 2 * HKV) * D * 2
+    us = time_graph(calls)
+    return {"kernel": kernel, "rows": rows, "us": round(us, 2), "bytes": nbytes, "GB/s": round(nbytes / us / 1e3, 1)}
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
-    ap.add_argument("--kernel", required=True, choices=["stream", "skinny", "cublas", "attn_decode", "attn_prefill"])
+    ap.add_argument("--kernel", required=True, choices=["stream", "skinny", "cublas", "attn_decode", "attn_prefill", "rmsnorm", "rope_store", "swiglu"])
     ap.add_argument("--shape", default="gateup", choices=sorted(SHAPES))
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--copies", type=int, default=12, help="copies of the weights the graph walks through")
@@ -130,7 +168,9 @@ def main(argv=None) -> int:
     from .ops import get_ops
     ops = get_ops(verbose=False)
     ops.set_dependent_launch(args.dependent_launch)
-    if args.kernel == "attn_prefill":
+    if args.kernel in ("rmsnorm", "rope_store", "swiglu"):
+        out = bench_rows(ops, args.kernel, args.rows)
+    elif args.kernel == "attn_prefill":
         out = bench_attn_prefill(ops, args.tokens, max(args.context, args.tokens), 32, 8, 128, args.layers)
     elif args.kernel == "attn_decode":
         out = bench_attn_decode(ops, args.rows, args.context, 32, 8, 128, args.layers)

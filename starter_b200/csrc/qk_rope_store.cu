@@ -96,43 +96,72 @@ qk_rope_store_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
     int slot, pos;
     row_place(batch, row, slot, pos);
     const int d0 = lane * 4, j0 = d0 & 63;
-    float c[4], sn[4];
+    __nv_bfloat162 c2[2], s2[2];
     {
         const uint2 craw = *reinterpret_cast<const uint2*>(cos_t + (long long)pos * 64 + j0);
         const uint2 sraw = *reinterpret_cast<const uint2*>(sin_t + (long long)pos * 64 + j0);
-        const __nv_bfloat162* ch = reinterpret_cast<const __nv_bfloat162*>(&craw);
-        const __nv_bfloat162* sh = reinterpret_cast<const __nv_bfloat162*>(&sraw);
-        const float2 c01 = __bfloat1622float2(ch[0]), c23 = __bfloat1622float2(ch[1]);
-        const float2 s01 = __bfloat1622float2(sh[0]), s23 = __bfloat1622float2(sh[1]);
-        c[0] = c01.x; c[1] = c01.y; c[2] = c23.x; c[3] = c23.y;
-        sn[0] = s01.x; sn[1] = s01.y; sn[2] = s23.x; sn[3] = s23.y;
+        c2[0] = reinterpret_cast<const __nv_bfloat162*>(&craw)[0];
+        c2[1] = reinterpret_cast<const __nv_bfloat162*>(&craw)[1];
+        s2[0] = reinterpret_cast<const __nv_bfloat162*>(&sraw)[0];
+        s2[1] = reinterpret_cast<const __nv_bfloat162*>(&sraw)[1];
     }
-    for (int head = warp; head < n_heads + n_kv_heads; head += 8) {
+    // A warp takes the heads warp, warp + 8, ...; it asks for the rows of up to QK_AHEAD of them (and the value rows that
+    // go with key heads) before it works on the first: one 256-byte row in flight per warp left the memory idle (26 us
+    // for 2,048 rows of the 4B shape, whose bytes need 8).
+    constexpr int QK_AHEAD = 5;
+    const int all_heads = n_heads + n_kv_heads;
+    for (int first = warp; first < all_heads; first += 8 * QK_AHEAD) {
+    uint2 raws[QK_AHEAD], vraws[QK_AHEAD];
+#pragma unroll
+    for (int u = 0; u < QK_AHEAD; ++u) {
+        const int head = first + 8 * u;
+        raws[u] = vraws[u] = make_uint2(0u, 0u);
+        if (head < all_heads) {
+            const __nv_bfloat16* src = qkv + (long long)row * width + (long long)head * 128;
+            raws[u] = *reinterpret_cast<const uint2*>(src + d0);
+            if (head >= n_heads) vraws[u] = *reinterpret_cast<const uint2*>(src + (long long)n_kv_heads * 128 + d0);
+        }
+    }
+#pragma unroll
+    for (int u = 0; u < QK_AHEAD; ++u) {
+        const int head = first + 8 * u;
+        if (head >= all_heads) break;
         const bool is_q = head < n_heads;
-        const __nv_bfloat16* src = qkv + (long long)row * width + (long long)head * 128;
         const W* w = is_q ? q_norm_w : k_norm_w;
-        const uint2 raw = *reinterpret_cast<const uint2*>(src + d0);
+        const uint2 raw = raws[u];
         const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-        const float2 v01 = __bfloat1622float2(h2[0]), v23 = __bfloat1622float2(h2[1]);
-        float y[4] = {v01.x, v01.y, v23.x, v23.y};
+        // The product of two bfloat16 numbers is exact in 32-bit, so a packed bfloat16 multiply (one rounding) gives
+        // the bits of "multiply in 32-bit, then round"; likewise the packed add of two rounded products.  Only the
+        // normalisation multiplies by a 32-bit factor and stays in 32-bit.
+        __nv_bfloat162 y2[2] = {h2[0], h2[1]};
         if (w != nullptr) {
-            float ss = y[0] * y[0];
-            ss = fmaf(y[1], y[1], ss); ss = fmaf(y[2], y[2], ss); ss = fmaf(y[3], y[3], ss);
+            const float2 v01 = __bfloat1622float2(h2[0]), v23 = __bfloat1622float2(h2[1]);
+            float ss = v01.x * v01.x;
+            ss = fmaf(v01.y, v01.y, ss); ss = fmaf(v23.x, v23.x, ss); ss = fmaf(v23.y, v23.y, ss);
             ss = warp_sum(ss);
             const float rstd = 1.0f / sqrtf(ss / 128.0f + eps);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const float n = rnd<__nv_bfloat16>(__fmul_rn(y[e], rstd));
-                y[e] = rnd<__nv_bfloat16>(__fmul_rn(to_f<W>(w[d0 + e]), n));
+            const __nv_bfloat162 n01 = __floats2bfloat162_rn(__fmul_rn(v01.x, rstd), __fmul_rn(v01.y, rstd));
+            const __nv_bfloat162 n23 = __floats2bfloat162_rn(__fmul_rn(v23.x, rstd), __fmul_rn(v23.y, rstd));
+            if (sizeof(W) == 2) {
+                const uint2 wraw = *reinterpret_cast<const uint2*>(w + d0);
+                const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+                y2[0] = __hmul2(w2[0], n01);
+                y2[1] = __hmul2(w2[1], n23);
+            } else {
+                const float2 f01 = __bfloat1622float2(n01), f23 = __bfloat1622float2(n23);
+                y2[0] = __floats2bfloat162_rn(__fmul_rn(to_f<W>(w[d0]), f01.x), __fmul_rn(to_f<W>(w[d0 + 1]), f01.y));
+                y2[1] = __floats2bfloat162_rn(__fmul_rn(to_f<W>(w[d0 + 2]), f23.x), __fmul_rn(to_f<W>(w[d0 + 3]), f23.y));
             }
         }
-        float o[4];
+        uint2 res;
+        __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const float partner = __shfl_xor_sync(0xffffffffu, y[e], 16);
-            const float a = rnd<__nv_bfloat16>(__fmul_rn(y[e], c[e]));
-            const float b = rnd<__nv_bfloat16>(__fmul_rn(lane < 16 ? -partner : partner, sn[e]));
-            o[e] = __fadd_rn(a, b);
+        for (int e = 0; e < 2; ++e) {
+            unsigned int partner = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<const unsigned int*>(&y2[e]), 16);
+            if (lane < 16) partner ^= 0x80008000u;          // the first half of a head meets minus its partner
+            const __nv_bfloat162 a = __hmul2(y2[e], c2[e]);
+            const __nv_bfloat162 b = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&partner), s2[e]);
+            r2[e] = __hadd2(a, b);
         }
         __nv_bfloat16* dst;
         if (is_q) {
@@ -144,14 +173,10 @@ qk_rope_store_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
                 continue;
             }
             dst = (__nv_bfloat16*)kv.k + off;
-            *reinterpret_cast<uint2*>((__nv_bfloat16*)kv.v + off + d0) =
-                *reinterpret_cast<const uint2*>(src + (long long)n_kv_heads * 128 + d0);
+            *reinterpret_cast<uint2*>((__nv_bfloat16*)kv.v + off + d0) = vraws[u];
         }
-        uint2 res;
-        __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
-        r2[0] = __floats2bfloat162_rn(o[0], o[1]);
-        r2[1] = __floats2bfloat162_rn(o[2], o[3]);
         *reinterpret_cast<uint2*>(dst + d0) = res;
+    }
     }
 }
 

@@ -465,3 +465,48 @@ def test_attention_respects_the_window_edge(ops, dtype, head_dim):
             got = a[-1, :head_dim].float()
             is_edge_value = float((got - value_at_edge).abs().max()) < 0.05 * float(value_at_edge.abs().max()) + 1e-3
             assert is_edge_value == inside, f"q_len {q_len}, key {'inside' if inside else 'outside'} the window"
+
+
+@pytest.mark.parametrize("width", [520, 1000, 2560, 3080, 4096])
+@pytest.mark.parametrize("wdtype", [torch.bfloat16, torch.float32])
+def test_rmsnorm_of_many_rows(ops, ref, width, wdtype):
+    """From 128 rows on the bfloat16 norm runs a warp per row (1 to 16 vectors of eight values per lane): same bits in
+    the residual sum, and the norm within a rounding step, for widths that fill the last vector and that do not."""
+    dtype, rows = torch.bfloat16, 301
+    x = rand((rows, width), dtype, 70, 3.0)
+    w = (1 + 0.1 * rand((width,), torch.float32, 71)).to(wdtype)
+    close(ops.rmsnorm(x, w, 1e-5), ref.rmsnorm(x, w, 1e-5), dtype, "rmsnorm", rel=8e-3)
+    d = rand((rows, width), dtype, 72)
+    x1, x2 = x.clone(), x.clone()
+    y1, y2 = ops.add_rmsnorm(x1, d, w, 1e-6), ref.add_rmsnorm(x2, d, w, 1e-6)
+    assert torch.equal(x1, x2), "residual sum"
+    close(y1, y2, dtype, "add_rmsnorm", rel=8e-3)
+    few = ops.add_rmsnorm(x.clone()[:7], d[:7], w, 1e-6)      # the block-per-row kernel on the same rows
+    assert float((few.float() - y1[:7].float()).abs().max()) <= 8e-3 * float(y1.float().abs().max())
+
+
+@pytest.mark.parametrize("heads,kv_heads", [(4, 2), (12, 3), (44, 4), (5, 1)])
+def test_rope_store_of_many_rows(ops, ref, heads, kv_heads):
+    """From 256 rows on, head size 128: a block per row, each warp with several heads' rows in flight.  Head counts
+    that fill the warps' turns and that do not, three sequences at unequal positions."""
+    dtype, D = torch.bfloat16, 128
+    caches = [Cache([KVRequest(kv_heads, D)], n_slots=3, max_tokens=64 * 10, dtype=dtype, device="cuda", max_step_tokens=400)
+              for _ in range(2)]
+    ang = torch.arange(500, dtype=torch.float32)[:, None] / (10000.0 ** (torch.arange(64).float() / 64))[None]
+    rotary = (ang.cos().to(dtype).cuda(), ang.sin().to(dtype).cuda(), D)
+    qn, kn = (1 + 0.1 * rand((D,), torch.float32, 100)).to(dtype), (1 + 0.1 * rand((D,), torch.float32, 101)).to(dtype)
+    q_lens, starts = (200, 70, 31), (0, 65, 130)
+    qkv = rand((sum(q_lens), (heads + 2 * kv_heads) * D), dtype, 102)
+    outs = []
+    for c, o in zip(caches, (ops, ref)):
+        slots = [c.alloc() for _ in q_lens]
+        for s, n, st in zip(slots, q_lens, starts):
+            c.assume_length(s, st)
+            c.reserve(s, st + n)
+        c.flush()
+        ctx = make_ctx(c, ops, slots, list(q_lens), dtype)
+        outs.append(o.qk_norm_rope_store(ctx, qkv, c.layers[0], heads, kv_heads, D, qn, kn, 1e-6, rotary))
+        assert int(ctx.status) == 0
+    close(outs[0], outs[1], dtype, "q", rel=8e-3)
+    close(caches[0].groups[0].k, caches[1].groups[0].k, dtype, "stored keys", rel=8e-3)
+    assert torch.equal(caches[0].groups[0].v, caches[1].groups[0].v)
