@@ -82,12 +82,28 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int first_page = lo_min / SB_PAGE, last_page = pos_max / SB_PAGE;
     const int n_pages = last_page - first_page + 1;
 
-    if (tid == 0) {
+    const int* table = kv.table + (long long)slot * kv.table_width;
+    if (tid == PT_ROWS) {
+        // The issuing thread sets the barriers up and asks for the first keys and values at once, so that they
+        // travel while the rows stage their queries and tensor memory is handed out.
 #pragma unroll
         for (int b = 0; b < 8; ++b) mbar_init(&bars[b], 1);
         mbar_init(p_ready, PT_ROWS);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int i = 0; i < 2 && i < n_pages; ++i) {
+            int lp = first_page + i;
+            if (kv.ring_pages) lp %= kv.ring_pages;
+            const int y = (max(table[lp], 0) * kv.n_kv_heads + kvh) * SB_PAGE;
+            mbar_expect_tx(&k_full[i], STAGE);
+            tma_load_2d(k_s + i * STAGE, &map_k, 0, y, &k_full[i]);
+            tma_load_2d(k_s + i * STAGE + KV_ATOM, &map_k, 64, y, &k_full[i]);
+            if (i == 0) {
+                mbar_expect_tx(&v_full[0], STAGE);
+                tma_load_2d(v_s, &map_v, 0, y, &v_full[0]);
+                tma_load_2d(v_s + KV_ATOM, &map_v, 64, y, &v_full[0]);
+            }
+        }
     }
     if (warp == 0) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)), "r"(256u) : "memory");
@@ -107,7 +123,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             *reinterpret_cast<uint4*>(q_s + (c >> 3) * Q_ATOM + tid * 128 + (((c & 7) ^ (tid & 7)) << 4)) = v;
         }
     }
-    const int* table = kv.table + (long long)slot * kv.table_width;
     // Ids of the block's pages: a ring of PT_IDS entries in two halves.  Both halves are filled at the start;
     // every 64 pages the rows refill the half whose pages are behind them with the pages 64 to 127 ahead.
     auto load_ids = [&](int first, int count) {
@@ -153,10 +168,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                            desc_k_major(kt + (ks >> 2) * KV_ATOM) + 2 * (ks & 3), idesc_s, ks > 0 ? 1u : 0u);
                 tc_commit(&s_done[i & 1]);
             };
-            issue_k(0);
-            issue_v(0);
-            if (n_pages > 1) issue_k(1);
-            issue_s(0);
+            issue_s(0);   // keys of pages 0 and 1 and values of page 0 were asked for at the block's start
             for (int i = 0; i < n_pages && !*abort_flag; ++i) {
                 const int b = i & 1;
                 // S of the next page: its buffer was read by the rows in iteration i - 1 (p_ready of i - 1, waited for below).
