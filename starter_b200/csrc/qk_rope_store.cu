@@ -80,9 +80,14 @@ __global__ void qk_rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
 }
 
 
-// The common case on the tensor-core path: bfloat16, head size 128, rotary over the whole head.  One block
-// per row, a warp per head in turns, four consecutive values per lane (8-byte accesses); the rotate-half
-// partner of a lane's values sits in lane ^ 16.
+// The common case on the tensor-core path: bfloat16, head size 128, rotary over the whole head.  A block takes rows in
+// turn (four blocks per SM at most); half a warp per head (eight consecutive values = 16 bytes per lane, the rotate-half partner of a lane's values in
+// lane ^ 8), so a warp works on two heads at once and on the heads 16 further in turns.  A warp asks for the rows
+// of all the heads of a turn (and the value rows that go with key heads) before it works on the first: one row in
+// flight per warp left the memory idle (26 us for 2,048 rows of the 4B shape, whose bytes need 8).
+// The product of two bfloat16 numbers is exact in 32-bit, so a packed bfloat16 multiply (one rounding) gives the
+// bits of "multiply in 32-bit, then round", and likewise the packed add of two rounded products; only the
+// normalisation multiplies by a 32-bit factor and stays in 32-bit.
 template <class W>
 __global__ void __launch_bounds__(256)
 qk_rope_store_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out, SbBatch batch, SbKV kv,
@@ -91,91 +96,94 @@ qk_rope_store_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
                           int* status) {
     pdl_wait();
     pdl_launch_dependents();   // the attention that follows looks up its pages and fetches old keys meanwhile
-    const int row = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int half = lane >> 4, hl = lane & 15;
     const int width = (n_heads + 2 * n_kv_heads) * 128;
-    int slot, pos;
-    row_place(batch, row, slot, pos);
-    const int d0 = lane * 4, j0 = d0 & 63;
-    __nv_bfloat162 c2[2], s2[2];
-    {
-        const uint2 craw = *reinterpret_cast<const uint2*>(cos_t + (long long)pos * 64 + j0);
-        const uint2 sraw = *reinterpret_cast<const uint2*>(sin_t + (long long)pos * 64 + j0);
-        c2[0] = reinterpret_cast<const __nv_bfloat162*>(&craw)[0];
-        c2[1] = reinterpret_cast<const __nv_bfloat162*>(&craw)[1];
-        s2[0] = reinterpret_cast<const __nv_bfloat162*>(&sraw)[0];
-        s2[1] = reinterpret_cast<const __nv_bfloat162*>(&sraw)[1];
-    }
-    // A warp takes the heads warp, warp + 8, ...; it asks for the rows of up to QK_AHEAD of them (and the value rows that
-    // go with key heads) before it works on the first: one 256-byte row in flight per warp left the memory idle (26 us
-    // for 2,048 rows of the 4B shape, whose bytes need 8).
-    constexpr int QK_AHEAD = 5;
+    for (int row = blockIdx.x; row < batch.n_rows; row += gridDim.x) {   // a block takes several rows in turn
+    int slot = 0, pos = 0;
+    const int d0 = hl * 8, j0 = d0 & 63;
+    uint4 craw, sraw;
+    const __nv_bfloat162* c2 = reinterpret_cast<const __nv_bfloat162*>(&craw);
+    const __nv_bfloat162* s2 = reinterpret_cast<const __nv_bfloat162*>(&sraw);
+    constexpr int QK_AHEAD = 3;
     const int all_heads = n_heads + n_kv_heads;
-    for (int first = warp; first < all_heads; first += 8 * QK_AHEAD) {
-    uint2 raws[QK_AHEAD], vraws[QK_AHEAD];
+    for (int base = 2 * warp; base < all_heads; base += 16 * QK_AHEAD) {
+        uint4 raws[QK_AHEAD], vraws[QK_AHEAD];
 #pragma unroll
-    for (int u = 0; u < QK_AHEAD; ++u) {
-        const int head = first + 8 * u;
-        raws[u] = vraws[u] = make_uint2(0u, 0u);
-        if (head < all_heads) {
-            const __nv_bfloat16* src = qkv + (long long)row * width + (long long)head * 128;
-            raws[u] = *reinterpret_cast<const uint2*>(src + d0);
-            if (head >= n_heads) vraws[u] = *reinterpret_cast<const uint2*>(src + (long long)n_kv_heads * 128 + d0);
+        for (int u = 0; u < QK_AHEAD; ++u) {
+            const int head = base + half + 16 * u;
+            raws[u] = vraws[u] = make_uint4(0u, 0u, 0u, 0u);
+            if (head < all_heads) {
+                const __nv_bfloat16* src = qkv + (long long)row * width + (long long)head * 128;
+                raws[u] = *reinterpret_cast<const uint4*>(src + d0);
+                if (head >= n_heads) vraws[u] = *reinterpret_cast<const uint4*>(src + (long long)n_kv_heads * 128 + d0);
+            }
         }
-    }
+        if (base == 2 * warp) {
+            // Where the row stands (three look-ups, each waiting for the one before) and its table entries are asked
+            // for after the row itself, which depends on none of them.
+            row_place(batch, row, slot, pos);
+            craw = *reinterpret_cast<const uint4*>(cos_t + (long long)pos * 64 + j0);
+            sraw = *reinterpret_cast<const uint4*>(sin_t + (long long)pos * 64 + j0);
+        }
 #pragma unroll
-    for (int u = 0; u < QK_AHEAD; ++u) {
-        const int head = first + 8 * u;
-        if (head >= all_heads) break;
-        const bool is_q = head < n_heads;
-        const W* w = is_q ? q_norm_w : k_norm_w;
-        const uint2 raw = raws[u];
-        const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
-        // The product of two bfloat16 numbers is exact in 32-bit, so a packed bfloat16 multiply (one rounding) gives
-        // the bits of "multiply in 32-bit, then round"; likewise the packed add of two rounded products.  Only the
-        // normalisation multiplies by a 32-bit factor and stays in 32-bit.
-        __nv_bfloat162 y2[2] = {h2[0], h2[1]};
-        if (w != nullptr) {
-            const float2 v01 = __bfloat1622float2(h2[0]), v23 = __bfloat1622float2(h2[1]);
-            float ss = v01.x * v01.x;
-            ss = fmaf(v01.y, v01.y, ss); ss = fmaf(v23.x, v23.x, ss); ss = fmaf(v23.y, v23.y, ss);
-            ss = warp_sum(ss);
-            const float rstd = 1.0f / sqrtf(ss / 128.0f + eps);
-            const __nv_bfloat162 n01 = __floats2bfloat162_rn(__fmul_rn(v01.x, rstd), __fmul_rn(v01.y, rstd));
-            const __nv_bfloat162 n23 = __floats2bfloat162_rn(__fmul_rn(v23.x, rstd), __fmul_rn(v23.y, rstd));
-            if (sizeof(W) == 2) {
-                const uint2 wraw = *reinterpret_cast<const uint2*>(w + d0);
-                const __nv_bfloat162* w2 = reinterpret_cast<const __nv_bfloat162*>(&wraw);
-                y2[0] = __hmul2(w2[0], n01);
-                y2[1] = __hmul2(w2[1], n23);
+        for (int u = 0; u < QK_AHEAD; ++u) {
+            const int head = base + half + 16 * u;
+            if (base + 16 * u >= all_heads) break;          // the same for both halves of the warp
+            const bool active = head < all_heads, is_q = head < n_heads;
+            const W* w = is_q ? q_norm_w : k_norm_w;
+            const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raws[u]);
+            __nv_bfloat162 y2[4] = {h2[0], h2[1], h2[2], h2[3]};
+            float f[8];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                const float2 v = __bfloat1622float2(h2[e]);
+                f[2 * e] = v.x;
+                f[2 * e + 1] = v.y;
+            }
+            float ss = 0.f;
+#pragma unroll
+            for (int e = 0; e < 8; ++e) ss = fmaf(f[e], f[e], ss);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);   // over the 16 lanes of the head
+            if (w != nullptr) {
+                const float rstd = 1.0f / sqrtf(ss / 128.0f + eps);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const __nv_bfloat162 n = __floats2bfloat162_rn(__fmul_rn(f[2 * e], rstd), __fmul_rn(f[2 * e + 1], rstd));
+                    if (sizeof(W) == 2) {
+                        y2[e] = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(w + d0 + 2 * e), n);
+                    } else {
+                        const float2 nf = __bfloat1622float2(n);
+                        y2[e] = __floats2bfloat162_rn(__fmul_rn(to_f<W>(w[d0 + 2 * e]), nf.x), __fmul_rn(to_f<W>(w[d0 + 2 * e + 1]), nf.y));
+                    }
+                }
+            }
+            uint4 res;
+            __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+                unsigned int partner = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<const unsigned int*>(&y2[e]), 8);
+                if (hl < 8) partner ^= 0x80008000u;          // the first half of a head meets minus its partner
+                const __nv_bfloat162 a = __hmul2(y2[e], c2[e]);
+                const __nv_bfloat162 b = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&partner), s2[e]);
+                r2[e] = __hadd2(a, b);
+            }
+            if (!active) continue;
+            __nv_bfloat16* dst;
+            if (is_q) {
+                dst = q_out + (long long)row * n_heads * 128 + (long long)head * 128;
             } else {
-                const float2 f01 = __bfloat1622float2(n01), f23 = __bfloat1622float2(n23);
-                y2[0] = __floats2bfloat162_rn(__fmul_rn(to_f<W>(w[d0]), f01.x), __fmul_rn(to_f<W>(w[d0 + 1]), f01.y));
-                y2[1] = __floats2bfloat162_rn(__fmul_rn(to_f<W>(w[d0 + 2]), f23.x), __fmul_rn(to_f<W>(w[d0 + 3]), f23.y));
+                const long long off = kv_offset(kv, slot, pos, head - n_heads);
+                if (off < 0) {
+                    if (hl == 0) atomicOr(status, SB_STATUS_NO_PAGE);
+                    continue;
+                }
+                dst = (__nv_bfloat16*)kv.k + off;
+                *reinterpret_cast<uint4*>((__nv_bfloat16*)kv.v + off + d0) = vraws[u];
             }
+            *reinterpret_cast<uint4*>(dst + d0) = res;
         }
-        uint2 res;
-        __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
-#pragma unroll
-        for (int e = 0; e < 2; ++e) {
-            unsigned int partner = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<const unsigned int*>(&y2[e]), 16);
-            if (lane < 16) partner ^= 0x80008000u;          // the first half of a head meets minus its partner
-            const __nv_bfloat162 a = __hmul2(y2[e], c2[e]);
-            const __nv_bfloat162 b = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&partner), s2[e]);
-            r2[e] = __hadd2(a, b);
-        }
-        __nv_bfloat16* dst;
-        if (is_q) {
-            dst = q_out + (long long)row * n_heads * 128 + (long long)head * 128;
-        } else {
-            const long long off = kv_offset(kv, slot, pos, head - n_heads);
-            if (off < 0) {
-                if (lane == 0) atomicOr(status, SB_STATUS_NO_PAGE);
-                continue;
-            }
-            dst = (__nv_bfloat16*)kv.k + off;
-            *reinterpret_cast<uint2*>((__nv_bfloat16*)kv.v + off + d0) = vraws[u];
-        }
-        *reinterpret_cast<uint2*>(dst + d0) = res;
     }
     }
 }
@@ -190,12 +198,13 @@ extern "C" int sb_qk_rope_store(int dtype, int wdtype, const void* qkv, void* q_
     if (kv.head_dim > QK_MAX_D || rotary_dim > kv.head_dim || (rotary_dim & 1)) return (int)cudaErrorInvalidValue;
     // (few rows, as in decode: a warp per head over many small blocks spreads over more SMs and is faster)
     if (dtype == SB_BF16 && kv.head_dim == 128 && rotary_dim == 128 && cos_t != nullptr && batch.n_rows >= 256) {
+        const int d128_blocks = batch.n_rows < 148 * 4 ? batch.n_rows : 148 * 4;
         if (wdtype == SB_F32)
-            sb_launch(qk_rope_store_d128_kernel<float>, batch.n_rows, 256, 0, stream, (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out,
+            sb_launch(qk_rope_store_d128_kernel<float>, d128_blocks, 256, 0, stream, (const __nv_bfloat16*)qkv, (__nv_bfloat16*)q_out,
                       batch, kv, n_heads, n_kv_heads, (const float*)q_norm_w, (const float*)k_norm_w, eps,
                       (const __nv_bfloat16*)cos_t, (const __nv_bfloat16*)sin_t, status);
         else
-            sb_launch(qk_rope_store_d128_kernel<__nv_bfloat16>, batch.n_rows, 256, 0, stream, (const __nv_bfloat16*)qkv,
+            sb_launch(qk_rope_store_d128_kernel<__nv_bfloat16>, d128_blocks, 256, 0, stream, (const __nv_bfloat16*)qkv,
                       (__nv_bfloat16*)q_out, batch, kv, n_heads, n_kv_heads, (const __nv_bfloat16*)q_norm_w,
                       (const __nv_bfloat16*)k_norm_w, eps, (const __nv_bfloat16*)cos_t, (const __nv_bfloat16*)sin_t, status);
         SB_LAUNCH_CHECK();
