@@ -30,6 +30,7 @@
 
 #include "common.cuh"
 #include "mma_utils.cuh"
+#include "qk_prep.cuh"
 
 namespace cg = cooperative_groups;
 
@@ -37,40 +38,6 @@ namespace cg = cooperative_groups;
 #define AD_KEYS_PER_WARP (SB_PAGE / AD_WARPS)  // 16
 #define AD_MAX_CLUSTER 8
 #define AD_MAX_DEVICES 64     // devices whose per-device set-up this file remembers
-
-// What the fused preparation needs besides the cache.  qkv [rows, (n_heads + 2 * n_kv_heads) * D], or
-// [rows, n_heads * D] when store_kv is 0 (a layer that reads another layer's cache); norm weights
-// bfloat16 or float (norm_f32), null = no per-head norm; cos/sin [positions, D / 2] bfloat16, null = no
-// rotary encoding (otherwise over the whole head).
-struct SbFusedQK {
-    const __nv_bfloat16* qkv;
-    const void* q_norm;
-    const void* k_norm;
-    const __nv_bfloat16* cos_t;
-    const __nv_bfloat16* sin_t;
-    int* status;
-    float eps;
-    int norm_f32;
-    int store_kv;
-    int reserved;
-    const void* next_w;        // a matrix (16-byte aligned) that the kernel after this one streams: asked into L2 when
-    long long next_bytes;      // this kernel's keys are read, so that memory stays busy through its merge; or null
-};
-
-__device__ __forceinline__ void unpack4(const uint2 raw, float (&v)[4]) {
-    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
-    const float2 a = __bfloat1622float2(h[0]), b = __bfloat1622float2(h[1]);
-    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
-}
-
-__device__ __forceinline__ void load_norm4(const void* w, int norm_f32, int d0, float (&v)[4]) {
-    if (norm_f32) {
-        const float4 f = *reinterpret_cast<const float4*>(reinterpret_cast<const float*>(w) + d0);
-        v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w;
-    } else {
-        unpack4(*reinterpret_cast<const uint2*>(reinterpret_cast<const __nv_bfloat16*>(w) + d0), v);
-    }
-}
 
 template <int D, bool FUSED, int AD_STAGES>
 __global__ void __launch_bounds__(AD_WARPS * 32)

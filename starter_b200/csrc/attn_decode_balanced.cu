@@ -13,17 +13,20 @@
 // results holds (pairs + blocks) entries whatever the lengths are.
 #include "common.cuh"
 #include "mma_utils.cuh"
+#include "qk_prep.cuh"
 
 #define AD_WARPS 4
 #define AD_STAGES 3
 #define AD_KEYS_PER_WARP (SB_PAGE / AD_WARPS)  // 16
 #define ADB_MAX_SEQS 1024
 
-template <int D>
+// FUSED: q is null and the queries come from the projection's rows: per-head norm, rotary encoding and the store of
+// the new key and value happen here (qk_prep.cuh), by the block whose share holds the pair's last page.
+template <int D, bool FUSED>
 __global__ void __launch_bounds__(AD_WARPS * 32, 1)
 attn_decode_balanced_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* __restrict__ out, SbBatch batch, SbKV kv,
                             int n_heads, float scale_log2, int window, float* __restrict__ partial,
-                            int* __restrict__ counters) {
+                            int* __restrict__ counters, SbFusedQK fused) {
     constexpr int CH = D / 8;                              // 16-byte chunks per row
     constexpr int SLICE = AD_KEYS_PER_WARP * D * 2;        // bytes of one warp's keys (or values) of a page
     constexpr int NT = D / 8;                              // output n-tiles of 8 columns
@@ -73,14 +76,21 @@ attn_decode_balanced_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
         const int p_begin = lo / SB_PAGE + page_in_pair;
         __syncthreads();   // the segment before this one is done with the shared memory
 
-        // Query heads of this kv head as rows of a 16-row tile, zero beyond G.
-        for (int i = tid; i < 16 * CH; i += AD_WARPS * 32) {
-            const int r = i / CH, c = i % CH;
-            uint4 v = make_uint4(0u, 0u, 0u, 0u);
-            if (r < G) v = *reinterpret_cast<const uint4*>(q + ((long long)row * n_heads + kvh * G + r) * D + c * 8);
-            *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
+        if (FUSED) {
+            // the share that ends with the pair's last page holds the new position: it stores the new key and value
+            const bool owns_new = fused.store_kv && page_in_pair + my_pages == pages_seq;
+            prepare_group<D, AD_WARPS>(fused, kv, q_s, row, kvh, n_heads, G, pos, owns_new,
+                                       owns_new ? kv_offset(kv, slot, pos, kvh) : -1);
+        } else {
+            // Query heads of this kv head as rows of a 16-row tile, zero beyond G.
+            for (int i = tid; i < 16 * CH; i += AD_WARPS * 32) {
+                const int r = i / CH, c = i % CH;
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (r < G) v = *reinterpret_cast<const uint4*>(q + ((long long)row * n_heads + kvh * G + r) * D + c * 8);
+                *reinterpret_cast<uint4*>(q_s + tile_off<D>(r, c)) = v;
+            }
         }
-        __syncthreads();
+        __syncthreads();   // the queries are in place; the new key and value are in the cache before their page is copied
         unsigned int qf[D / 16][4];
     #pragma unroll
         for (int ks = 0; ks < D / 16; ++ks)
@@ -311,8 +321,9 @@ attn_decode_balanced_kernel(const __nv_bfloat16* __restrict__ q, __nv_bfloat16* 
     }
 }
 
-template <int D> static int launch_balanced(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale,
-                                            int window, int grid, float* partial, int* counters, cudaStream_t stream) {
+template <int D, bool FUSED>
+static int launch_balanced(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale, int window, int grid,
+                           float* partial, int* counters, SbFusedQK fused, cudaStream_t stream) {
     const int pipe_bytes = AD_WARPS * AD_STAGES * 2 * AD_KEYS_PER_WARP * D * 2;
     const int merge_bytes = (AD_WARPS * 16 * D + 2 * AD_WARPS * 16) * 4;
     // More than half an SM's shared memory is asked for, so that no SM ever holds two of these blocks: the
@@ -320,15 +331,23 @@ template <int D> static int launch_balanced(const void* q, void* out, SbBatch ba
     // before it still holds some SMs.
     const int need = 16 * D * 2 + (pipe_bytes > merge_bytes ? pipe_bytes : merge_bytes);
     const int smem = need > 116 * 1024 ? need : 116 * 1024;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_balanced_kernel<D>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    static bool configured[64] = {};   // the attribute belongs to the kernel as loaded on one device
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return (int)cudaErrorInvalidDevice;
+    if (!configured[device]) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_balanced_kernel<D, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
-        configured = true;
+        configured[device] = true;
     }
-    sb_launch(attn_decode_balanced_kernel<D>, grid, AD_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
-              batch, kv, n_heads, scale * 1.4426950408889634f, window, partial, counters);
+    sb_launch(attn_decode_balanced_kernel<D, FUSED>, grid, AD_WARPS * 32, smem, stream, (const __nv_bfloat16*)q, (__nv_bfloat16*)out,
+              batch, kv, n_heads, scale * 1.4426950408889634f, window, partial, counters, fused);
     return (int)cudaGetLastError();
+}
+
+static bool balanced_shape_ok(const SbBatch& batch, const SbKV& kv, int n_heads, int grid) {
+    return kv.n_kv_heads > 0 && n_heads > 0 && batch.n_rows == batch.n_seqs && n_heads % kv.n_kv_heads == 0 &&
+           n_heads / kv.n_kv_heads <= 16 && grid >= 1 && grid <= 512 && batch.n_seqs <= ADB_MAX_SEQS &&
+           (kv.head_dim == 64 || kv.head_dim == 128);
 }
 
 extern "C" {
@@ -340,12 +359,22 @@ extern "C" {
 int sb_attn_decode_balanced(const void* q, void* out, SbBatch batch, SbKV kv, int n_heads, float scale, int window,
                             int grid, float* partial, int* counters, cudaStream_t stream) {
     if (batch.n_seqs <= 0) return 0;
-    if (batch.n_rows != batch.n_seqs || n_heads % kv.n_kv_heads || n_heads / kv.n_kv_heads > 16 || grid < 1 ||
-        grid > 512 || batch.n_seqs > ADB_MAX_SEQS)
+    if (!balanced_shape_ok(batch, kv, n_heads, grid)) return (int)cudaErrorInvalidValue;
+    SbFusedQK none = {};
+    if (kv.head_dim == 128) return launch_balanced<128, false>(q, out, batch, kv, n_heads, scale, window, grid, partial, counters, none, stream);
+    return launch_balanced<64, false>(q, out, batch, kv, n_heads, scale, window, grid, partial, counters, none, stream);
+}
+
+// The same with the preparation of q and k inside: qkv is the row of the fused projection; the new key and value
+// are stored in the cache by this call.
+int sb_attn_decode_balanced_fused(SbFusedQK fused, void* out, SbBatch batch, SbKV kv, int n_heads, float scale, int window,
+                                  int grid, float* partial, int* counters, cudaStream_t stream) {
+    if (batch.n_seqs <= 0) return 0;
+    if (!balanced_shape_ok(batch, kv, n_heads, grid) || fused.qkv == nullptr || fused.status == nullptr ||
+        ((fused.cos_t == nullptr) != (fused.sin_t == nullptr)))
         return (int)cudaErrorInvalidValue;
-    if (kv.head_dim == 128) return launch_balanced<128>(q, out, batch, kv, n_heads, scale, window, grid, partial, counters, stream);
-    if (kv.head_dim == 64) return launch_balanced<64>(q, out, batch, kv, n_heads, scale, window, grid, partial, counters, stream);
-    return (int)cudaErrorInvalidValue;
+    if (kv.head_dim == 128) return launch_balanced<128, true>(nullptr, out, batch, kv, n_heads, scale, window, grid, partial, counters, fused, stream);
+    return launch_balanced<64, true>(nullptr, out, batch, kv, n_heads, scale, window, grid, partial, counters, fused, stream);
 }
 
 }  // extern "C"

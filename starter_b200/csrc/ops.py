@@ -89,6 +89,8 @@ class Ops:
             "sb_attn_decode_balanced": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
                                         c_void_p],
             "sb_attn_decode": [c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p, c_void_p],
+            "sb_attn_decode_balanced_fused": [SbFusedQK, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p,
+                                              c_void_p, c_void_p],
             "sb_attn_decode_fused": [SbFusedQK, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_int, c_void_p, c_void_p,
                                      c_void_p],
             "sb_argmax": [c_void_p, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p],
@@ -409,15 +411,33 @@ class Ops:
             self._scratch[key] = buf
         return buf
 
-    def _split_decode(self, ctx, kv, n_heads) -> bool:
-        """True when a step is served by the split-key decode kernel: one token per sequence, bfloat16 cache with head
-        size 64 or 128, at most 16 query heads per kv head, and no more (sequence, kv head) pairs than blocks fit at once."""
+    def _decode_route(self, ctx, kv, n_heads):
+        """Which decode kernel serves a step of one token per sequence (bfloat16 cache with head size 64 or 128, at most
+        16 query heads per kv head): "split" (a grid of (sequence, kv head, split)) or, when there are more (sequence,
+        kv head) pairs than blocks fit at once, "balanced" (one block per SM, equal shares of all pages); None when the
+        step is of another kind."""
         if kv.head_dim not in (64, 128) or n_heads % kv.n_kv_heads or n_heads // kv.n_kv_heads > 16:
-            return False
+            return None
         if not (ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs):
-            return False
+            return None
         pairs = ctx.n_seqs * kv.n_kv_heads
-        return not (self.decode_balanced and pairs > self.decode_resident(kv.head_dim) and ctx.n_seqs <= 1024)
+        if self.decode_balanced and pairs > self.decode_resident(kv.head_dim) and ctx.n_seqs <= 1024:
+            return "balanced"
+        return "split"
+
+    def _split_decode(self, ctx, kv, n_heads) -> bool:
+        return self._decode_route(ctx, kv, n_heads) == "split"
+
+    def _balanced_scratch(self, device, ctx, kv, n_heads):
+        grid = min(self.sm_count(), 512)
+        key = ("attn_decode_balanced", device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, grid)
+        buf = self._scratch.get(key)
+        if buf is None:
+            pairs = ctx.n_seqs * kv.n_kv_heads
+            floats = (pairs + grid) * (n_heads // kv.n_kv_heads) * (kv.head_dim + 2)
+            buf = self._scratch[key] = (torch.empty(floats, dtype=torch.float32, device=device),
+                                        torch.zeros(pairs, dtype=torch.int32, device=device))
+        return grid, buf
 
     def qk_attention(self, ctx, qkv, layer_cache, n_heads, n_kv_heads, head_dim, q_norm, k_norm, eps, rotary, scale, window,
                      then=None):
@@ -427,7 +447,8 @@ class Ops:
         if not self.fuse_qk or qkv.dtype != torch.bfloat16 or layer_cache.group.k.dtype != torch.bfloat16:
             return None
         kv = self._kv(layer_cache)
-        if kv.head_dim != head_dim or (n_kv_heads and kv.n_kv_heads != n_kv_heads) or not self._split_decode(ctx, kv, n_heads):
+        route = self._decode_route(ctx, kv, n_heads)
+        if kv.head_dim != head_dim or (n_kv_heads and kv.n_kv_heads != n_kv_heads) or route is None:
             return None
         if qkv.shape[1] != (n_heads + 2 * n_kv_heads) * head_dim:
             raise KernelError("qk_attention: qkv has the wrong width")
@@ -457,6 +478,12 @@ class Ops:
         fused = SbFusedQK(_ptr(qkv), _ptr(q_norm), _ptr(k_norm), _ptr(cos), _ptr(sin), _ptr(ctx.status), float(eps), norm_f32,
                           int(n_kv_heads > 0), 0, next_w, next_bytes)
         out = torch.empty((qkv.shape[0], n_heads * head_dim), dtype=qkv.dtype, device=qkv.device)
+        if route == "balanced":
+            grid, buf = self._balanced_scratch(qkv.device, ctx, kv, n_heads)
+            self._check(self.lib.sb_attn_decode_balanced_fused(fused, _ptr(out), self._batch(ctx), kv, n_heads, scale,
+                                                               int(window or 0), grid, _ptr(buf[0]), _ptr(buf[1]),
+                                                               self._stream()), "attn_decode_balanced_fused")
+            return out
         n_splits = self.decode_splits(ctx.n_seqs, kv.n_kv_heads, layer_cache.group.table_width, kv.head_dim)
         partial, counters = self._decode_scratch(qkv.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, n_splits)
         self._check(self.lib.sb_attn_decode_fused(fused, _ptr(out), self._batch(ctx), kv, n_heads, scale, int(window or 0),
@@ -478,14 +505,7 @@ class Ops:
             split = decode and self._split_decode(ctx, kv, n_heads)
             if decode and not split:
                 # More pairs than blocks fit at once: one block per SM, each with an equal share of all pages.
-                grid = min(self.sm_count(), 512)
-                key = ("attn_decode_balanced", q.device, ctx.n_seqs, n_heads, kv.n_kv_heads, kv.head_dim, grid)
-                buf = self._scratch.get(key)
-                if buf is None:
-                    pairs = ctx.n_seqs * kv.n_kv_heads
-                    floats = (pairs + grid) * (n_heads // kv.n_kv_heads) * (kv.head_dim + 2)
-                    buf = self._scratch[key] = (torch.empty(floats, dtype=torch.float32, device=q.device),
-                                                torch.zeros(pairs, dtype=torch.int32, device=q.device))
+                grid, buf = self._balanced_scratch(q.device, ctx, kv, n_heads)
                 self._check(self.lib.sb_attn_decode_balanced(_ptr(q), _ptr(out), self._batch(ctx), kv, n_heads, scale,
                                                              int(window or 0), grid, _ptr(buf[0]), _ptr(buf[1]),
                                                              self._stream()), "attn_decode_balanced")

@@ -248,7 +248,7 @@ def test_decode_attention(ops, ref, monkeypatch, heads, kv_heads, head_dim, wind
         assert float((outs[0][-1, :head_dim].float() - want).abs().max()) < 0.05 * float(want.abs().max())
 
 
-@pytest.mark.parametrize("splits", [1, 3, 8, 11])
+@pytest.mark.parametrize("splits", [None, 1, 3, 8, 11])
 @pytest.mark.parametrize("heads,kv_heads,head_dim,window,norm,rotary,store", [
     (8, 2, 128, None, torch.bfloat16, True, True), (16, 1, 64, None, torch.float32, True, True),
     (6, 3, 64, 100, None, True, True), (4, 4, 128, 700, torch.bfloat16, False, True),
@@ -259,8 +259,11 @@ def test_decode_attention_with_preparation_inside(ops, ref, monkeypatch, heads, 
     torch restatement: the attention's output and what it left in the cache.  Lengths put the new token at
     the start of a page, at its end, and in a sequence's first position."""
     dtype = torch.bfloat16
-    monkeypatch.setattr(ops, "decode_balanced", False)
-    monkeypatch.setattr(ops, "decode_splits", lambda *a: splits)
+    if splits is None:   # the balanced kernel (equal shares of all pages per block), with the preparation inside as well
+        monkeypatch.setattr(ops, "decode_resident", lambda *a: 0)
+    else:
+        monkeypatch.setattr(ops, "decode_balanced", False)
+        monkeypatch.setattr(ops, "decode_splits", lambda *a: splits)
     cache = Cache([KVRequest(kv_heads, head_dim, window)], n_slots=6, max_tokens=64 * 60, dtype=dtype, device="cuda",
                   max_seq_tokens=1600, max_step_tokens=64)
     g = cache.groups[0]
