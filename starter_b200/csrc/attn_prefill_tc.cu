@@ -215,8 +215,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             // This thread's row of scores: mask (only where the page is not wholly visible), maximum, probabilities.
             const int key0 = (first_page + i) * SB_PAGE;
             float s[SB_PAGE];
-            tc_ld32(tmem_row + b * SB_PAGE, s);
-            tc_ld32(tmem_row + b * SB_PAGE + 32, s + 32);
+            {
+                uint32_t* raw = reinterpret_cast<uint32_t*>(s);   // both halves asked for, then one wait
+                tc_ld32_async(tmem_row + b * SB_PAGE, raw);
+                tc_ld32_async(tmem_row + b * SB_PAGE + 32, raw + 32);
+                tc_wait_ld();
+            }
             tc_fence_before();   // ordered before the arrival below, after which the issuer may overwrite this buffer
             const bool whole_page_visible = key0 + SB_PAGE - 1 <= pos_min && key0 >= lo_max && t_last == t0 + PT_ROWS - 1;
             if (!whole_page_visible) {
