@@ -16,7 +16,7 @@
 #include "qk_prep.cuh"
 
 #define AD_WARPS 4
-#define AD_STAGES 3
+#define AD_STAGES 4
 #define AD_KEYS_PER_WARP (SB_PAGE / AD_WARPS)  // 16
 #define ADB_MAX_SEQS 1024
 

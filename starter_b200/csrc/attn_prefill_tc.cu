@@ -56,7 +56,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     uint32_t* tmem_slot = (uint32_t*)(bars + 9);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
     int* s_pages = (int*)(tmem_slot + 4);          // [PT_IDS] ids of the block's next pages
-    pdl_wait();
     if ((smem_u32(smem) & 1023u) != 0) {           // the swizzled tiles need it; never seen, but never assumed
         if (threadIdx.x == 0) atomicOr(status, SB_STATUS_TIMEOUT);
         return;
@@ -83,6 +82,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     const int n_pages = last_page - first_page + 1;
 
     const int* table = kv.table + (long long)slot * kv.table_width;
+    // Up to here only the batch's description and the lengths were read, which the kernel before this one (the
+    // rotary encoding and cache store) does not write; from here on its queries, keys and values are.
+    pdl_wait();
     if (tid == PT_ROWS) {
         // The issuing thread sets the barriers up and asks for the first keys and values at once, so that they
         // travel while the rows stage their queries and tensor memory is handed out.

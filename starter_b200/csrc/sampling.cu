@@ -49,16 +49,32 @@ __global__ void argmax_kernel(const float* __restrict__ values, const int* __res
     __shared__ int best_i[32];
     const int chunks = gridDim.y;
     pdl_wait();
-    const int per = (n + chunks - 1) / chunks;
-    const int begin = blockIdx.y * per, end = min(n, begin + per);
+    const int per = (((n + chunks - 1) / chunks) + 3) & ~3;   // slices start at multiples of four values
+    const int begin = min(n, (int)blockIdx.y * per), end = min(n, begin + per);
     const float* row = values + (long long)blockIdx.x * row_stride;
     const int* idx = indices ? indices + (long long)blockIdx.x * row_stride : nullptr;
     float bv = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
-        const float v = row[i];
-        const int id = idx ? idx[i] : i;
-        if (bi == 0x7fffffff || v > bv || (v == bv && id < bi)) { bv = v; bi = id; }
+    if (idx == nullptr && (row_stride & 3) == 0 && (reinterpret_cast<uintptr_t>(values) & 15) == 0) {
+        // four values per load; a thread sees its indices in rising order, so ">" keeps the lowest index of equals
+        const int end4 = begin + ((end - begin) & ~3);
+        for (int i = begin + threadIdx.x * 4; i < end4; i += blockDim.x * 4) {
+            const float4 v = *reinterpret_cast<const float4*>(row + i);
+            if (bi == 0x7fffffff || v.x > bv) { bv = v.x; bi = i; }
+            if (v.y > bv) { bv = v.y; bi = i + 1; }
+            if (v.z > bv) { bv = v.z; bi = i + 2; }
+            if (v.w > bv) { bv = v.w; bi = i + 3; }
+        }
+        for (int i = end4 + threadIdx.x; i < end; i += blockDim.x) {
+            const float v = row[i];
+            if (bi == 0x7fffffff || v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+        }
+    } else {
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+            const float v = row[i];
+            const int id = idx ? idx[i] : i;
+            if (bi == 0x7fffffff || v > bv || (v == bv && id < bi)) { bv = v; bi = id; }
+        }
     }
     block_best(bv, bi, best_v, best_i);
     if (threadIdx.x == 0) {
