@@ -35,6 +35,15 @@
 #define PT_IDS 128
 #define PT_THREADS 160   // four warps of rows and the issuer's warp
 
+#ifdef SB_TIMELINE
+// Tuning builds only: clock stamps of one block's issuer and of its first row, per page: [page][8].
+static __device__ long long* pt_timeline = nullptr;
+extern "C" int sb_attn_prefill_tc_timeline(long long* p) { return (int)cudaMemcpyToSymbol(pt_timeline, &p, sizeof(p)); }
+#define PT_STAMP(page, what) do { if (pt_timeline && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0 && (page) < 64) pt_timeline[(page) * 8 + (what)] = clock64(); } while (0)
+#else
+#define PT_STAMP(page, what) ((void)0)
+#endif
+
 
 __global__ void __launch_bounds__(PT_THREADS, 2)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -173,13 +182,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             issue_s(0);   // keys of pages 0 and 1 and values of page 0 were asked for at the block's start
             for (int i = 0; i < n_pages && !*abort_flag; ++i) {
                 const int b = i & 1;
-                // S of the next page: its buffer was read by the rows in iteration i - 1 (p_ready of i - 1, waited for below).
-                if (i + 1 < n_pages) issue_s(i + 1);
-                if (i + 2 < n_pages) {   // keys two pages ahead go into the stage of page i, once S has read it
+                // Keys two pages ahead go into the stage of page i, once S of page i has read it.  That product was
+                // issued an iteration ago, so the wait is over; the copy is asked for before the next product is issued,
+                // because issuing blocks for as long as the tensor core works on the block's earlier products.
+                if (i + 2 < n_pages) {
                     mbar_wait(&s_done[b], (i >> 1) & 1, abort_flag, status);
                     issue_k(i + 2);
                 }
+                // S of the next page: its buffer was read by the rows in iteration i - 1 (p_ready of i - 1, waited for
+                // below), and the product that read P from it was issued before this one.
+                if (i + 1 < n_pages) issue_s(i + 1);
+                PT_STAMP(i, 0);
                 mbar_wait(p_ready, i & 1, abort_flag, status);        // P of page i is written (and O rescaled if need be)
+                PT_STAMP(i, 1);
                 mbar_wait(&v_full[b], (i >> 1) & 1, abort_flag, status);
                 if (*abort_flag) break;
                 tc_fence_after();
@@ -189,6 +204,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     tc_mma_ts(tmem + O_COL, tmem + b * SB_PAGE + 8 * ks, desc_mn_major(vt + ks * 2048, KV_ATOM), idesc_o,
                               (i > 0 || ks > 0) ? 1u : 0u);
                 tc_commit(&o_done[b]);
+                PT_STAMP(i, 2);
                 if (i + 1 < n_pages) {   // values of the next page go into the stage of page i - 1, once its product is done
                     if (i > 0) mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, status);
                     issue_v(i + 1);
@@ -210,9 +226,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
         for (int i = 0; i < n_pages; ++i) {
             const int b = i & 1;
             if (i > 0 && (i & 63) == 0) load_ids(i + 64, 64);   // read by the issuer 62 pages (and as many barriers) from now
+            if (tid == 0) PT_STAMP(i, 7);
             mbar_wait(&s_done[b], (i >> 1) & 1, abort_flag, status);
             if (*abort_flag) break;
             tc_fence_after();
+            if (tid == 0) PT_STAMP(i, 3);
 
             // This thread's row of scores: mask (only where the page is not wholly visible), maximum, probabilities.
             const int key0 = (first_page + i) * SB_PAGE;
@@ -224,6 +242,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 tc_wait_ld();
             }
             tc_fence_before();   // ordered before the arrival below, after which the issuer may overwrite this buffer
+            if (tid == 0) PT_STAMP(i, 4);
             const bool whole_page_visible = key0 + SB_PAGE - 1 <= pos_min && key0 >= lo_max && t_last == t0 + PT_ROWS - 1;
             if (!whole_page_visible) {
 #pragma unroll
@@ -293,9 +312,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             // P goes where this row's S was: 64 bfloat16 = 32 columns of the S buffer, which the product reads as its
             // operand A straight from tensor memory.  (The tensor core runs a block's products in the order they were
             // issued: S of page i + 2, which overwrites this buffer, is issued after O += P V of page i.)
+            if (tid == 0) PT_STAMP(i, 5);
             tc_st32_u32(tmem_row + b * SB_PAGE, reinterpret_cast<const uint32_t*>(packed));
             tc_fence_before();
             mbar_arrive(p_ready);
+            if (tid == 0) PT_STAMP(i, 6);
         }
         if (!*abort_flag) {   // the last product, then this row's output
             mbar_wait(&o_done[(n_pages - 1) & 1], ((n_pages - 1) >> 1) & 1, abort_flag, status);
