@@ -1,5 +1,5 @@
 // Weight-streaming matrix product for a handful of rows (decode): C[M,N] = A[M,K] * W[N,K]^T,
-// bfloat16 in, 32-bit accumulate, M <= 16.
+// bfloat16 in, 32-bit accumulate, M <= 32.
 //
 // Reference: engine/kernels/gemm.py:60-112 (one M tile, persistent grid over N tiles and K
 // splits, 32-bit partial sums reduced afterwards) and :212-256 (CUDA-core GEMV for M <= 4).
@@ -57,7 +57,7 @@ __device__ __forceinline__ float silu_mul_bf16(float g, float u) {
 // What a warp reads in one turn is then one contiguous piece of 4 KB instead of sixteen pieces of 256 bytes a row
 // apart, which memory serves faster (measured on the 4B shapes: the decode step 3.7% shorter at batch 8, 6.8% at batch 1).
 template <int NT, bool GATE_UP, bool TILED, int WARPS, bool CLUSTER>
-__global__ void __launch_bounds__(WARPS * 32, WARPS == 8 ? 4 : 8)
+__global__ void __launch_bounds__(WARPS * 32, (WARPS == 8 ? 4 : 8) / (NT > 2 ? 2 : 1))   // 64 registers; 128 from 17 rows on
 gemm_skinny_kernel(const __nv_bfloat16* __restrict__ A, const __nv_bfloat16* __restrict__ W, void* __restrict__ C,
                    int M, int n_out, int K, int k_per_split, int n_splits, int out_f32,
                    float* __restrict__ partial, int* __restrict__ counters) {
@@ -247,17 +247,17 @@ extern "C" {
 // Scratch for n_splits > 1: partial sums (floats) and one counter per row block (ints, zero before
 // the first launch; the kernel leaves them zero).
 long long sb_gemm_skinny_scratch_floats(int M, int n_out, int n_splits, int gate_up) {
-    const int nt = M <= 8 ? 1 : 2;
+    const int nt = (M + 7) / 8;
     const long long blocks = (n_out + GS_ROWS - 1) / GS_ROWS;
     return n_splits > 1 ? blocks * n_splits * (gate_up ? 2 : 1) * GS_ROWS * 8 * nt : 0;
 }
 
 // A [M, K], W [n_out, K] (or [2 * n_out, K] with gate_up), C [M, n_out] bfloat16 or float.
-// Takes M <= 16 and K a multiple of 8; k_per_split a multiple of 128.  tiled: W is the tile-major copy (see above).
+// Takes M <= 32 and K a multiple of 8; k_per_split a multiple of 128.  tiled: W is the tile-major copy (see above).
 int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int K, int n_splits, int k_per_split,
                    int gate_up, int out_f32, int tiled, int warps, float* partial, int* counters, cudaStream_t stream) {
     if (M <= 0 || n_out <= 0) return 0;
-    if (M > 16 || (K & 7) || n_splits < 1 || n_splits > 65535 || (k_per_split % GS_KWARP) ||
+    if (M > 32 || (K & 7) || n_splits < 1 || n_splits > 65535 || (k_per_split % GS_KWARP) ||
         (long long)k_per_split * n_splits < K || (warps != 4 && warps != 8))
         return (int)cudaErrorInvalidValue;
     dim3 grid((n_out + GS_ROWS - 1) / GS_ROWS, n_splits);
@@ -284,8 +284,12 @@ int sb_gemm_skinny(const void* A, const void* W, void* C, int M, int n_out, int 
     } while (0)
     if (M <= 8) {
         if (gate_up) SB_SKINNY(1, true); else SB_SKINNY(1, false);
-    } else {
+    } else if (M <= 16) {
         if (gate_up) SB_SKINNY(2, true); else SB_SKINNY(2, false);
+    } else if (M <= 24) {
+        if (gate_up) SB_SKINNY(3, true); else SB_SKINNY(3, false);
+    } else {
+        if (gate_up) SB_SKINNY(4, true); else SB_SKINNY(4, false);
     }
 #undef SB_SKINNY
 #undef SB_SKINNY2

@@ -225,7 +225,11 @@ class Ops:
 
     # ---- products -----------------------------------------------------------------------
 
-    SKINNY_MAX_ROWS = 8   # up to 16 run, but cuBLAS is faster from 9 rows on
+    # The mma.sync product takes up to 32 rows.  Measured in the step (B200): to 16 rows it beats cuBLAS + the SwiGLU
+    # kernel (1.7B sizes at batch 16: 1.84 -> 1.76 ms a step, 4B sizes: 3.89 -> 3.82 ms), from 17 rows on it needs 128
+    # registers and loses (4B sizes at batch 32: 6.64 against 5.35 ms).
+    SKINNY_MAX_ROWS = int(os.environ.get("STARTER_B200_SKINNY_MAX_ROWS", 16))
+    STREAM_MIN_ROWS = 9   # the TMA + tcgen05 product serves the output head from here on
     STREAM_MAX_ROWS = 64
     STREAM_MIN_WORK = int(os.environ.get("STARTER_B200_STREAM_MIN", 300_000_000))  # elements of W below which the simpler kernels do as well
 
@@ -279,8 +283,8 @@ class Ops:
         """Measured on a B200 (microbench.py): per launch the TMA-fed kernel pays about 9 us before and
         after it streams (set-up, first data, the pass through scratch for shared tiles) and then streams
         at 6.3-6.9 TB/s; the warp-level kernel pays about 3 us and streams at 4.7 TB/s, more on very large
-        matrices, and takes at most 8 rows.  So: the output head for 9 to 64 rows, nothing smaller."""
-        return (self.use_stream and self.SKINNY_MAX_ROWS < M <= (32 if gate_up else self.STREAM_MAX_ROWS)
+        matrices.  So: the output head for 9 to 64 rows, nothing smaller."""
+        return (self.use_stream and self.STREAM_MIN_ROWS <= M <= (32 if gate_up else self.STREAM_MAX_ROWS)
                 and K % 8 == 0 and K >= 64 and n_out * K * (2 if gate_up else 1) >= self.STREAM_MIN_WORK)
 
     def skinny_splits(self, blocks: int, K: int) -> int:
@@ -290,12 +294,12 @@ class Ops:
         gain in parallelism; 1 slice for q/k/v, output and gate/up, 3 for down)."""
         return max(1, min(round(3 * self.sm_count() / blocks), K // 3072))
 
-    def skinny_warps(self, n_blocks: int) -> int:
-        """Warps per block.  Eight-warp blocks fit four to an SM; when the blocks number a little more than
-        that (608 for 592 places), the few left over run as a second wave on an empty GPU.  Four-warp blocks
-        fit eight to an SM, so the same blocks run at once."""
-        resident8 = 4 * self.sm_count()
-        return 4 if resident8 < n_blocks <= 2 * resident8 else 8
+    def skinny_warps(self, n_blocks: int, nt: int = 1) -> int:
+        """Warps per block.  Eight-warp blocks fit four to an SM (two from 17 rows on, where the kernel takes 128
+        registers); when the blocks number a little more than that (608 for 592 places), the few left over run as a
+        second wave on an empty GPU.  Four-warp blocks fit twice as many to an SM, so the same blocks run at once."""
+        resident8 = (4 if nt <= 2 else 2) * self.sm_count()
+        return 4 if resident8 < n_blocks <= (2 if nt <= 2 else 2.2) * resident8 else 8
 
     def _skinny(self, a, w, n_out, gate_up, out_float32):
         """The weight-streaming product for a handful of rows (see gemm_skinny.cu)."""
@@ -304,15 +308,16 @@ class Ops:
         want = self.skinny_splits(blocks, K) if self.force_skinny is None else self.force_skinny[0]
         k_per_split = -(-K // want // 128) * 128 if want > 1 else -(-K // 128) * 128
         n_splits = -(-K // k_per_split)
-        key = ("gemm_skinny", a.device, M > 8, n_out, n_splits, gate_up)
+        nt = -(-M // 8)   # activation tiles of 8 rows
+        key = ("gemm_skinny", a.device, nt, n_out, n_splits, gate_up)
         buf = self._scratch.get(key)
         if buf is None:
-            floats = blocks * n_splits * (2 if gate_up else 1) * 16 * (8 if M <= 8 else 16) if n_splits > 1 else 1
+            floats = blocks * n_splits * (2 if gate_up else 1) * 16 * 8 * nt if n_splits > 1 else 1
             buf = (torch.empty(floats, dtype=torch.float32, device=a.device),
                    torch.zeros(blocks, dtype=torch.int32, device=a.device))
             self._scratch[key] = buf
         out = torch.empty((M, n_out), dtype=torch.float32 if out_float32 else torch.bfloat16, device=a.device)
-        warps = self.skinny_warps(blocks * n_splits) if self.force_skinny is None or len(self.force_skinny) < 3 else self.force_skinny[2]
+        warps = self.skinny_warps(blocks * n_splits, -(-M // 8)) if self.force_skinny is None or len(self.force_skinny) < 3 else self.force_skinny[2]
         copy = getattr(w, "_sb_tiled", None)
         if copy is not None and (copy[1] != (2 if gate_up else 1) or (self.force_skinny is not None and not self.force_skinny[1])):
             copy = None   # tiled for the other pairing of rows, or a test asks for the row-major path
@@ -325,8 +330,8 @@ class Ops:
     def linear(self, a, w, out_float32=False):
         """a [M, K] times w [N, K] transposed -> [M, N] in a's dtype, or 32-bit when asked.
 
-        float32: this library's CUDA-core product, always.  bfloat16: the weight-streaming kernel for up
-        to 16 rows, cuBLAS for large products, the CUDA-core product for what is left."""
+        float32: this library's CUDA-core product, always.  bfloat16: the weight-streaming kernels for up
+        to 16 rows (and for the output head up to 64), cuBLAS for larger products, the CUDA-core product for what is left."""
         M, K = a.shape
         N = w.shape[0]
         if w.shape[1] != K or a.dtype != w.dtype:

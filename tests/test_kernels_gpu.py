@@ -305,7 +305,7 @@ def test_decode_attention_with_preparation_inside(ops, ref, monkeypatch, heads, 
         assert torch.equal(k_got.nan_to_num(), k0.nan_to_num())
 
 
-@pytest.mark.parametrize("M", [1, 5, 8, 11, 16])
+@pytest.mark.parametrize("M", [1, 5, 8, 11, 16, 19, 24, 29, 32])
 @pytest.mark.parametrize("splits,tiled,warps", [(1, False, 8), (3, False, 8), (2, True, 8), (1, True, 4), (2, False, 4), (8, False, 4),
                                                 (11, False, 8), (3, True, 8), (11, True, 4), (5, True, 8), (6, False, 4), (7, True, 4)])
 def test_skinny_product_variants(ops, ref, M, splits, tiled, warps):
