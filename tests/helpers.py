@@ -12,8 +12,10 @@ from plain import qwen3_plain as plain
 # Largest |difference| allowed, as a fraction of the largest |logit| of the plain implementation.
 # float32: both sides are true 32-bit, the orders of summation differ.  bfloat16: both sides round
 # at the same places, but a sum that lands on the other side of a rounding edge moves a value by
-# one bfloat16 step (2^-8 relative), and a few of those meet in a logit.
-TOLERANCE = {"float32": 1e-4, "bfloat16": 3e-2}
+# one bfloat16 step (2^-8 relative), and a few of those meet in a logit.  Measured over the tiny
+# configurations in every cutting: 0.003 to 0.010 of the scale; the reference allows itself 0.03
+# against another implementation (tests/test_engine.py:50-53 there).
+TOLERANCE = {"float32": 1e-4, "bfloat16": 2e-2}
 
 
 def make_session(folder, dtype, ops=None, device=None, **kw):
