@@ -87,7 +87,9 @@ __global__ void qk_rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ 
 // flight per warp left the memory idle (26 us for 2,048 rows of the 4B shape, whose bytes need 8).
 // The product of two bfloat16 numbers is exact in 32-bit, so a packed bfloat16 multiply (one rounding) gives the
 // bits of "multiply in 32-bit, then round", and likewise the packed add of two rounded products; only the
-// normalisation multiplies by a 32-bit factor and stays in 32-bit.
+// normalisation multiplies by a 32-bit factor and stays in 32-bit.  The _rn forms matter: the plain ones may be
+// contracted into one fused multiply-add, which drops the rounding of the first product (a fifth of the values then
+// differ from the formula by one step).
 template <class W>
 __global__ void __launch_bounds__(256)
 qk_rope_store_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* __restrict__ q_out, SbBatch batch, SbKV kv,
@@ -152,7 +154,7 @@ qk_rope_store_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
                 for (int e = 0; e < 4; ++e) {
                     const __nv_bfloat162 n = __floats2bfloat162_rn(__fmul_rn(f[2 * e], rstd), __fmul_rn(f[2 * e + 1], rstd));
                     if (sizeof(W) == 2) {
-                        y2[e] = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(w + d0 + 2 * e), n);
+                        y2[e] = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(w + d0 + 2 * e), n);
                     } else {
                         const float2 nf = __bfloat1622float2(n);
                         y2[e] = __floats2bfloat162_rn(__fmul_rn(to_f<W>(w[d0 + 2 * e]), nf.x), __fmul_rn(to_f<W>(w[d0 + 2 * e + 1]), nf.y));
@@ -165,9 +167,9 @@ qk_rope_store_d128_kernel(const __nv_bfloat16* __restrict__ qkv, __nv_bfloat16* 
             for (int e = 0; e < 4; ++e) {
                 unsigned int partner = __shfl_xor_sync(0xffffffffu, *reinterpret_cast<const unsigned int*>(&y2[e]), 8);
                 if (hl < 8) partner ^= 0x80008000u;          // the first half of a head meets minus its partner
-                const __nv_bfloat162 a = __hmul2(y2[e], c2[e]);
-                const __nv_bfloat162 b = __hmul2(*reinterpret_cast<const __nv_bfloat162*>(&partner), s2[e]);
-                r2[e] = __hadd2(a, b);
+                const __nv_bfloat162 a = __hmul2_rn(y2[e], c2[e]);
+                const __nv_bfloat162 b = __hmul2_rn(*reinterpret_cast<const __nv_bfloat162*>(&partner), s2[e]);
+                r2[e] = __hadd2_rn(a, b);
             }
             if (!active) continue;
             __nv_bfloat16* dst;

@@ -137,6 +137,9 @@ def test_store_and_attention(ops, ref, dtype, heads, kv_heads, head_dim, window)
             assert int(ctx.status) == 0
             outs.append((q, a))
         close(outs[0][0], outs[1][0], dtype, f"q after norm and rope, step {step}", rel=1e-5 if dtype == torch.float32 else 8e-3)
+        if dtype == torch.bfloat16:   # the kernel rounds where the formula rounds: (nearly) every value has its bits
+            same = float((outs[0][0] == outs[1][0]).float().mean())
+            assert same >= 0.998, f"only {same:.5f} of q's values have the restatement's bits"
         close(outs[0][1], outs[1][1], dtype, f"attention, step {step}")
         close(caches[0].groups[0].k, caches[1].groups[0].k, dtype, "stored keys", rel=1e-5 if dtype == torch.float32 else 8e-3)
         assert torch.equal(caches[0].groups[0].v, caches[1].groups[0].v), "stored values"
@@ -484,6 +487,8 @@ def test_rmsnorm_of_many_rows(ops, ref, width, wdtype):
     y1, y2 = ops.add_rmsnorm(x1, d, w, 1e-6), ref.add_rmsnorm(x2, d, w, 1e-6)
     assert torch.equal(x1, x2), "residual sum"
     close(y1, y2, dtype, "add_rmsnorm", rel=8e-3)
+    same = float((y1 == y2).float().mean())       # the same roundings: only a last bit of the sum of squares can move a value
+    assert same >= 0.999, f"only {same:.5f} of the normed values have the restatement's bits"
     few = ops.add_rmsnorm(x.clone()[:7], d[:7], w, 1e-6)      # the block-per-row kernel on the same rows
     assert float((few.float() - y1[:7].float()).abs().max()) <= 8e-3 * float(y1.float().abs().max())
 
@@ -513,3 +518,7 @@ def test_rope_store_of_many_rows(ops, ref, heads, kv_heads):
     close(outs[0], outs[1], dtype, "q", rel=8e-3)
     close(caches[0].groups[0].k, caches[1].groups[0].k, dtype, "stored keys", rel=8e-3)
     assert torch.equal(caches[0].groups[0].v, caches[1].groups[0].v)
+    # The kernel rounds where the formula rounds (five roundings a value), so nearly every value has the restatement's
+    # bits; the rest sit one bfloat16 step away, where the two sums of squares differ in their last bit.
+    same = float((outs[0] == outs[1]).float().mean())
+    assert same >= 0.995, f"only {same:.5f} of the values have the restatement's bits"
