@@ -251,11 +251,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                     if (!(n <= pos && n >= lo)) s[c] = -INFINITY;
                 }
             }
-            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains instead of one of 64 steps
+            float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains of three-input maxima
 #pragma unroll
-            for (int c = 0; c < SB_PAGE; c += 4) {
-                mx4[0] = fmaxf(mx4[0], s[c]); mx4[1] = fmaxf(mx4[1], s[c + 1]);
-                mx4[2] = fmaxf(mx4[2], s[c + 2]); mx4[3] = fmaxf(mx4[3], s[c + 3]);
+            for (int c = 0; c < SB_PAGE; c += 8) {
+                mx4[0] = max_of_three(mx4[0], s[c], s[c + 1]); mx4[1] = max_of_three(mx4[1], s[c + 2], s[c + 3]);
+                mx4[2] = max_of_three(mx4[2], s[c + 4], s[c + 5]); mx4[3] = max_of_three(mx4[3], s[c + 6], s[c + 7]);
             }
             const float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3])) * scale_log2;   // scale_log2 > 0: the maximum commutes with it
             float alpha = 1.0f;
@@ -266,18 +266,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
             }
             const float m_use = m_ref == -INFINITY ? 0.f : m_ref;
             uint4 packed[SB_PAGE / 8];
-            float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+            // The rows' time is their instruction count: scale-and-shift and the running sums work on pairs.
+            const float2 scale2 = make_float2(scale_log2, scale_log2), shift2 = make_float2(-m_use, -m_use);
+            float2 sum2[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
             for (int c = 0; c < SB_PAGE; c += 8) {
                 __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&packed[c >> 3]);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) {
-                    const float p0 = fast_exp2(fmaf(s[c + 2 * e], scale_log2, -m_use)), p1 = fast_exp2(fmaf(s[c + 2 * e + 1], scale_log2, -m_use));
-                    sum4[e] += p0 + p1;
-                    h2[e] = __floats2bfloat162_rn(p0, p1);
+                    const float2 x = fma_pair(make_float2(s[c + 2 * e], s[c + 2 * e + 1]), scale2, shift2);
+                    const float2 pr = make_float2(fast_exp2(x.x), fast_exp2(x.y));
+                    sum2[e] = add_pair(sum2[e], pr);
+                    h2[e] = __floats2bfloat162_rn(pr.x, pr.y);
                 }
             }
-            l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+            l_run = l_run * alpha + (((sum2[0].x + sum2[0].y) + (sum2[1].x + sum2[1].y)) + ((sum2[2].x + sum2[2].y) + (sum2[3].x + sum2[3].y)));
 
             // The accumulator of earlier pages moves to the new reference (rare after the first pages): O += P V of
             // the page before must be done before it is rescaled.
