@@ -538,7 +538,7 @@ def run_reference(args, raw, workload) -> int:
                    "head_dim": raw["head_dim"], "intermediate": raw["intermediate_size"], "vocab": raw["vocab_size"],
                    "tied": raw["tie_word_embeddings"], "global_batch": batch, "seq_len": context,
                    "prompts": workload["prompts"], "prefill_tokens": PREFILL_TOKENS, "parallelism": "single GPU",
-                   "cuda_graphs": True, "peaks": peak_source,
+                   "cuda_graphs": True, "l2": "each step reads all weights (larger than L2)", "peaks": peak_source,
                    "switches": f"ENGINE_RECYCLE={os.environ['ENGINE_RECYCLE']} ENGINE_SELF_CHECK={os.environ['ENGINE_SELF_CHECK']}",
                    "value_is": "its captured decode graph replayed with plan.pos set; e2e is Engine.generate alone"},
         "e2e": {"value": round(e2e_value, 1), "unit": "tokens/s", "h2d_bytes_per_step": 0,

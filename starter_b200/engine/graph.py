@@ -162,15 +162,26 @@ class GraphDecoder:
         A sequence that has ended stops reading its cache with the next step that is launched; its
         slot stays held until the caller frees it."""
         sess = self.session
-        cache = sess.cache
         sampling = self.default_sampling if sampling is None else sampling
         if sampling.greedy != self.greedy:
             raise ValueError("this decoder's graphs were captured for the other kind of token selection")
         n = len(slots)
         last = list(tokens)
         live = list(range(n))          # sequences still decoding, in the order of the bucket's rows
-        done_steps = 0
         self.history = []
+        try:
+            yield from self._run(slots, last, live, request_ids, first_step, n_steps, stop, sampling)
+        finally:
+            # However the loop ends (all steps handed out, every sequence stopped, the caller gone, an error): the
+            # device finishes what is in flight before the caller frees the slots those steps still write to.
+            torch.cuda.current_stream(sess.device).synchronize()
+        sess.stepper.raise_on_status()
+
+    def _run(self, slots, last, live, request_ids, first_step, n_steps, stop, sampling):
+        sess = self.session
+        cache = sess.cache
+        n = len(slots)
+        done_steps = 0
         while live and done_steps < n_steps:
             b = self.bucket(len(live))
             cache.flush()
@@ -222,4 +233,3 @@ class GraphDecoder:
             record[1] = launched
             done_steps += yielded
             live = [i for i in rows if i in alive]
-        sess.stepper.raise_on_status()
