@@ -397,14 +397,28 @@ class Ops:
         return (2 if head_dim > 64 else 4) * self.sm_count()
 
     def decode_splits(self, n_seqs: int, n_kv_heads: int, max_pages: int, head_dim: int = 128) -> int:
-        """How many blocks share one (sequence, kv head).  Measured on a B200 at a context of 4,096: about
-        256 blocks in all is best (more blocks mean shorter shares, and a share pays fixed costs: loading
-        the queries, merging the warps, the pass through scratch memory), never more than 16 per pair.
-        A function of shapes only, so that a captured graph stays valid as sequences grow."""
+        """How many blocks share one (sequence, kv head).  Measured on a B200 at a context of 4,096 with 8 kv heads,
+        in the whole decode step (ms a step for splits 2 / 4 / 6 / 8 / 16):
+          batch 1 (8 pairs):   - / 2.32 / 2.18 / 2.13 / 2.16        batch 2 (16 pairs): 2.68 / 2.30 / 2.19 / 2.60 / 2.28
+          batch 4 (32 pairs): - / 2.38 / 2.41 (5) / 2.79 / 2.71     batch 8 (64 pairs): 2.80 / 2.81 / 3.14 / 3.39 / 3.51
+          batch 16 (128 pairs): 2 splits 3.80, 3 splits 4.16        batch 32 (256 pairs): 1 split 5.33, 2 splits 5.50
+        About 64 to 128 blocks in all is best while the pairs are few (every block then has an SM and the deeper
+        pipeline to itself, and a share pays its fixed costs once: loading the queries, merging the warps, meeting
+        the other shares); clusters of 7 or 8 blocks are slow as soon as there are 16 or more of them (7 splits at
+        batch 2: 2.65 ms), so beyond 8 pairs a pair has 6 splits at most.  A function of shapes only, so that a
+        captured graph stays valid as sequences grow."""
         if os.environ.get("STARTER_B200_ATTN_SPLITS"):   # a tuning override; the kernel refuses what its merge cannot hold
             return max(1, min(int(os.environ["STARTER_B200_ATTN_SPLITS"]), 256))
         pairs = max(n_seqs * n_kv_heads, 1)
-        return max(1, min(256 // pairs, 16, max_pages, self.decode_resident(head_dim) // pairs))
+        if pairs <= 8:
+            want = 8
+        elif pairs <= 16:
+            want = 6
+        elif pairs <= 32:
+            want = 4
+        else:
+            want = 256 // pairs
+        return max(1, min(want, max_pages, self.decode_resident(head_dim) // pairs))
 
     def _decode_scratch(self, device, n_seqs, n_heads, n_kv_heads, head_dim, n_splits):
         key = ("attn_decode", device, n_seqs, n_heads, n_kv_heads, head_dim, n_splits)
