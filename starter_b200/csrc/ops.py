@@ -411,11 +411,13 @@ class Ops:
             return max(1, min(int(os.environ["STARTER_B200_ATTN_SPLITS"]), 256))
         pairs = max(n_seqs * n_kv_heads, 1)
         if pairs <= 8:
-            want = 8
+            want = 8 if max_pages <= 96 else 16     # a cache of 16,384 tokens a sequence: 2.44 ms with 16, 2.65 with 8
         elif pairs <= 16:
             want = 6
         elif pairs <= 32:
             want = 4
+        elif pairs <= 64:
+            want = 4 if max_pages <= 96 else 2      # batch 8 at 16,384 tokens: 4.83 ms with 2, 4.99 with 4, 5.78 with 8
         else:
             want = 256 // pairs
         return max(1, min(want, max_pages, self.decode_resident(head_dim) // pairs))
