@@ -79,7 +79,9 @@ class Ops:
                                  c_float, c_void_p, c_void_p, c_int, c_void_p, c_void_p],
             "sb_attention_general": [c_int, c_void_p, c_void_p, SbBatch, SbKV, c_int, c_float, c_int, c_void_p],
             "sb_gemm_skinny": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
-                               c_void_p, c_void_p, c_void_p],
+                               c_int, c_void_p, c_void_p, c_void_p, c_void_p],
+            "sb_gemm_skinny_normed": [c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                      c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p],
             "sb_tile_matrix": [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
             "sb_gemm_stream": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p,
                                c_void_p, c_void_p],
@@ -301,8 +303,30 @@ class Ops:
         resident8 = (4 if nt <= 2 else 2) * self.sm_count()
         return 4 if resident8 < n_blocks <= (2 if nt <= 2 else 2.2) * resident8 else 8
 
-    def _skinny(self, a, w, n_out, gate_up, out_float32):
-        """The weight-streaming product for a handful of rows (see gemm_skinny.cu)."""
+    # Rows up to which a layer's norms and residual sums run inside its products (gemm_skinny.cuh) instead of in the
+    # norm kernel.  Off: measured in the decode step on a B200 (4B layer sizes, context 4,096), the fold removes 72
+    # of 259 launches and still loses: batch 1: 2.155 -> 2.194 ms a step, batch 8: 2.810 -> 2.889, batch 16: 3.765 ->
+    # 4.301.  Every block of 16 weight rows norms all the activation rows again (608 blocks do the work of 8), and
+    # that costs more than the launch it saves (about 2 us: a step without any norm is 0.12 to 0.15 ms shorter).
+    FOLD_MAX_ROWS = int(os.environ.get("STARTER_B200_FOLD_MAX_ROWS", 0))
+
+    def folds(self, rows: int, dtype) -> bool:
+        """Whether a step of this many rows should hand its norms and residual sums to ``linear`` and
+        ``linear_swiglu`` (``norm=``, ``add_to=``).  The decode product can take them for bfloat16, up to 16 rows
+        and inner sizes that are multiples of 8."""
+        return dtype == torch.bfloat16 and rows <= min(self.FOLD_MAX_ROWS, self.SKINNY_MAX_ROWS, 16)
+
+    def _can_fold(self, rows: int, dtype, K: int) -> bool:
+        return dtype == torch.bfloat16 and rows <= min(self.SKINNY_MAX_ROWS, 16) and K % 8 == 0
+
+    def _skinny(self, a, w, n_out, gate_up, out_float32, norm=None, add_to=None):
+        """The weight-streaming product for a handful of rows (see gemm_skinny.cuh).
+
+        norm: (weight, eps) or (weight, eps, stats) of an RMSNorm to take of a's rows first; stats is what the product
+        that wrote a left behind (below), without it every block reads the rows once more.
+        add_to: a bfloat16 [M, n_out] tensor that the product is added to, or an object with such a tensor as ``x``
+        and a field ``stats`` (a residual stream), which then receives the statistics of the new rows: the sums of
+        squares of each 16 columns, [M, ceil(n_out / 16)] floats."""
         M, K = a.shape
         blocks = -(-n_out // 16)
         want = self.skinny_splits(blocks, K) if self.force_skinny is None else self.force_skinny[0]
@@ -316,26 +340,53 @@ class Ops:
             buf = (torch.empty(floats, dtype=torch.float32, device=a.device),
                    torch.zeros(blocks, dtype=torch.int32, device=a.device))
             self._scratch[key] = buf
-        out = torch.empty((M, n_out), dtype=torch.float32 if out_float32 else torch.bfloat16, device=a.device)
+        stats_out = None
+        if add_to is not None:
+            out = add_to.x if hasattr(add_to, "stats") else add_to
+            if out_float32 or out.dtype != torch.bfloat16 or tuple(out.shape) != (M, n_out) or not out.is_contiguous():
+                raise KernelError(f"the product adds to a contiguous bfloat16 [{M}, {n_out}] tensor")
+            if out is not add_to:
+                stats_out = torch.empty((M, blocks), dtype=torch.float32, device=a.device)
+        else:
+            out = torch.empty((M, n_out), dtype=torch.float32 if out_float32 else torch.bfloat16, device=a.device)
         warps = self.skinny_warps(blocks * n_splits, -(-M // 8)) if self.force_skinny is None or len(self.force_skinny) < 3 else self.force_skinny[2]
         copy = getattr(w, "_sb_tiled", None)
         if copy is not None and (copy[1] != (2 if gate_up else 1) or (self.force_skinny is not None and not self.force_skinny[1])):
             copy = None   # tiled for the other pairing of rows, or a test asks for the row-major path
         src = copy[0] if copy is not None else w
-        self._check(self.lib.sb_gemm_skinny(_ptr(a), _ptr(src), _ptr(out), M, n_out, K, n_splits, k_per_split, int(gate_up),
-                                            int(out_float32), int(copy is not None), warps, _ptr(buf[0]), _ptr(buf[1]),
-                                            self._stream()), "gemm_skinny")
+        tail = (M, n_out, K, n_splits, k_per_split, int(gate_up), int(out_float32), int(copy is not None), warps,
+                int(add_to is not None), _ptr(stats_out), _ptr(buf[0]), _ptr(buf[1]), self._stream())
+        if norm is None:
+            self._check(self.lib.sb_gemm_skinny(_ptr(a), _ptr(src), _ptr(out), *tail), "gemm_skinny")
+        else:
+            gamma, eps, stats = norm if len(norm) == 3 else (*norm, None)
+            if M > 16 or gamma.dtype != torch.bfloat16 or gamma.numel() != K:
+                raise KernelError(f"the norm folded into a product takes up to 16 rows and a bfloat16 weight of {K} values")
+            if stats is not None and (stats.dtype != torch.float32 or tuple(stats.shape) != (M, -(-K // 16))):
+                raise KernelError(f"the rows' statistics are [{M}, {-(-K // 16)}] floats, not {tuple(stats.shape)} {stats.dtype}")
+            self._check(self.lib.sb_gemm_skinny_normed(_ptr(a), _ptr(gamma), float(eps), _ptr(stats), _ptr(src), _ptr(out),
+                                                       *tail), "gemm_skinny_normed")
+        if stats_out is not None:
+            add_to.stats = stats_out
         return out
 
-    def linear(self, a, w, out_float32=False):
+    def linear(self, a, w, out_float32=False, norm=None, add_to=None):
         """a [M, K] times w [N, K] transposed -> [M, N] in a's dtype, or 32-bit when asked.
 
         float32: this library's CUDA-core product, always.  bfloat16: the weight-streaming kernels for up
-        to 16 rows (and for the output head up to 64), cuBLAS for larger products, the CUDA-core product for what is left."""
+        to 16 rows (and for the output head up to 64), cuBLAS for larger products, the CUDA-core product for what is left.
+
+        norm=(weight, eps[, statistics]): the product of the RMSNorm of a's rows; add_to=x: x += product, in place, x
+        returned (see ``_skinny``).  Both for bfloat16 and up to 16 rows: the decode product takes them in its prologue
+        and epilogue; ``folds`` says whether that pays."""
         M, K = a.shape
         N = w.shape[0]
         if w.shape[1] != K or a.dtype != w.dtype:
             raise KernelError(f"linear: a is {tuple(a.shape)} {a.dtype}, w is {tuple(w.shape)} {w.dtype}")
+        if norm is not None or add_to is not None:
+            if not self._can_fold(M, a.dtype, K):
+                raise KernelError(f"linear: no folded norm or sum for {M} rows of {K} {a.dtype} values")
+            return self._skinny(a, w, N, False, out_float32, norm, add_to)
         if a.dtype == torch.bfloat16 and K % 8 == 0:
             if self._takes_stream(M, N, K, False):
                 return self._stream_product(a, w, N, False, out_float32)
@@ -350,9 +401,13 @@ class Ops:
                                              _ptr(out), M, N, K, self._stream()), "gemm_general")
         return out
 
-    def linear_swiglu(self, h, w_gate_up):
-        """swiglu(h @ w_gate_up^T) for a fused [gate; up] matrix: [M, K] -> [M, rows / 2]."""
+    def linear_swiglu(self, h, w_gate_up, norm=None):
+        """swiglu(h @ w_gate_up^T) for a fused [gate; up] matrix: [M, K] -> [M, rows / 2].  norm: as in ``linear``."""
         M, K = h.shape
+        if norm is not None:
+            if not self._can_fold(M, h.dtype, K) or h.dtype != w_gate_up.dtype:
+                raise KernelError(f"linear_swiglu: no folded norm for {M} rows of {K} {h.dtype} values")
+            return self._skinny(h, w_gate_up, w_gate_up.shape[0] // 2, True, False, norm)
         if h.dtype == torch.bfloat16 and w_gate_up.dtype == torch.bfloat16 and K % 8 == 0:
             if self._takes_stream(M, w_gate_up.shape[0] // 2, K, True):
                 return self._stream_product(h, w_gate_up, w_gate_up.shape[0] // 2, True, False)

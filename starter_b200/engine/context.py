@@ -62,16 +62,20 @@ class ResidualStream:
     The sum x + pending is taken in 32-bit inside the kernel that also norms it
     (the reference's add_rms_norm, engine/kernels/add_rmsnorm.py:16-29), so a
     branch's output meets the residual in the same pass that feeds the next branch.
+    A branch whose last product can add to x itself is given the stream as the
+    place to add to (``ops.linear(..., add_to=stream)``) and pushes nothing.
     """
 
     def __init__(self, x: torch.Tensor):
         self.x = x
         self.pending = None
+        self.stats = None   # left by a product that added its result to x itself: what a norm folded into the next product reads
 
     def normed(self, norm) -> torch.Tensor:
         if self.pending is None:
             return norm.forward(self.x)
         delta, self.pending = self.pending, None
+        self.stats = None   # x changes here
         return norm.add_forward(self.x, delta)
 
     def push(self, branch_output: torch.Tensor) -> None:

@@ -61,6 +61,7 @@ class Attention:
         self.q_norm = weights.get("q_norm")
         self.k_norm = weights.get("k_norm")
         self.position = build_part("position", spec.position, {}, runtime) if spec.position is not None else None
+        self.takes_fold = spec.hidden_size % 8 == 0 and (spec.num_heads * spec.head_dim) % 8 == 0
         self.fused_position = self.position is None or hasattr(self.position, "fused_rotary")
         if not self.fused_position and not hasattr(self.position, "apply"):
             raise ValueError("a position part offers fused_rotary() or apply(ctx, q, k)")
@@ -90,14 +91,19 @@ class Attention:
             pieces += [k.reshape(rows, hkv * d), qkv[:, (hq + hkv) * d:]]
         return torch.cat(pieces, dim=1).contiguous()
 
-    def forward(self, ctx, h, layer_cache):
-        qkv = self.ops.linear(h, self.w_qkv)
+    def _out(self, a, residual):
+        return self.ops.linear(a, self.w_o) if residual is None else self.ops.linear(a, self.w_o, add_to=residual)
+
+    def forward(self, ctx, h, layer_cache, norm=None, residual=None):
+        """h is the normed input; with ``norm`` it is the residual itself and the norm is taken inside the q/k/v
+        product; with ``residual`` the output projection adds to that tensor instead of returning its own."""
+        qkv = self.ops.linear(h, self.w_qkv) if norm is None else self.ops.linear(h, self.w_qkv, norm=norm)
         if not self.fused_position:
             n_kv = self.num_kv_heads if self.stores_kv else 0
             q = self.ops.qk_norm_rope_store(ctx, self._positions_applied(ctx, qkv), layer_cache, self.num_heads, n_kv,
                                             self.head_dim, None, None, 0.0, None)
             a = self.ops.attention(ctx, q, layer_cache, self.num_heads, self.scale, self.window)
-            return self.ops.linear(a, self.w_o)
+            return self._out(a, residual)
         rotary = self.position.fused_rotary() if self.position is not None else None
         n_kv = self.num_kv_heads if self.stores_kv else 0
         a = None
@@ -109,7 +115,7 @@ class Attention:
             q = self.ops.qk_norm_rope_store(ctx, qkv, layer_cache, self.num_heads, n_kv, self.head_dim,
                                             self.q_norm, self.k_norm, self.norm_eps, rotary)
             a = self.ops.attention(ctx, q, layer_cache, self.num_heads, self.scale, self.window)
-        return self.ops.linear(a, self.w_o)
+        return self._out(a, residual)
 
 
 register_part("mixer", "attention", Attention)

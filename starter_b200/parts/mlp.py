@@ -29,13 +29,18 @@ class GatedMLP:
         self.ops = runtime.ops
         self.w_gate_up = self.ops.prepare_matrix(torch.cat([weights["gate"], weights["up"]], dim=0), halves=2)
         self.w_down = self.ops.prepare_matrix(weights["down"])
+        self.takes_fold = spec.hidden_size % 8 == 0 and spec.intermediate_size % 8 == 0
 
     def prepare(self, cache) -> None:
         pass
 
-    def forward(self, ctx, h):
-        act = self.ops.linear_swiglu(h, self.w_gate_up)
-        return self.ops.linear(act, self.w_down)
+    def forward(self, ctx, h, norm=None, residual=None):
+        """h is the normed input; with ``norm`` it is the residual itself and the norm is taken inside the first
+        product; with ``residual`` the result is added to that tensor instead of being returned on its own."""
+        if norm is None and residual is None:
+            return self.ops.linear(self.ops.linear_swiglu(h, self.w_gate_up), self.w_down)
+        act = self.ops.linear_swiglu(h, self.w_gate_up, norm=norm)
+        return self.ops.linear(act, self.w_down, add_to=residual)
 
 
 register_part("ff", "gated_mlp", GatedMLP)

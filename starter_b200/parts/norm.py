@@ -28,5 +28,10 @@ class RMSNorm:
         """x += delta in place (32-bit sum, stored in x's dtype), then the norm of the new x."""
         return self.ops.add_rmsnorm(x, delta, self.weight, self.eps)
 
+    def folded(self, dtype):
+        """(weight, eps) for a product that takes this norm in its prologue (``ops.linear(..., norm=)``), or None when
+        the weight is kept in another type than the rows (a 32-bit weight in a bfloat16 run: the norm runs on its own)."""
+        return (self.weight, self.eps) if self.weight.dtype == dtype else None
+
 
 register_part("norm", "rmsnorm", RMSNorm)

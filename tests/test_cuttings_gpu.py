@@ -52,12 +52,13 @@ def test_dependent_launch_changes_no_bit(tiny_folders, dtype):
     assert_close(got[True][:3], plain_logits(folder, seqs, dtype), dtype, "dependent launch")
 
 
-@pytest.mark.parametrize("route", ["stream", "balanced", "slices"])
+@pytest.mark.parametrize("route", ["stream", "balanced", "slices", "folded", "folded slices"])
 def test_other_kernel_routes_through_the_whole_engine(tiny_folders, monkeypatch, route):
     """The shape rules send the test configurations to a few of the kernels only.  Here the rules are bent so
     that the whole engine runs on the others: the TMA + tcgen05 product for every matrix (batches of 12), the
     balanced decode attention (with the separate q/k kernel before it), and K slices / key splits that meet in
-    clusters.  Freed pages are poisoned between batches."""
+    clusters; and the decode products that take the norm before them and the residual sum after them into
+    themselves (off by default: slower than the norm kernel as measured).  Freed pages are poisoned between batches."""
     from starter_b200.csrc.ops import get_ops
     ops = get_ops(verbose=False)
     if route == "stream":
@@ -67,10 +68,22 @@ def test_other_kernel_routes_through_the_whole_engine(tiny_folders, monkeypatch,
     elif route == "balanced":
         monkeypatch.setattr(ops, "decode_resident", lambda *a: 0)
         batch = 5
-    else:
+    elif route == "slices":
         monkeypatch.setattr(ops, "skinny_splits", lambda blocks, K: 3)
         monkeypatch.setattr(ops, "decode_splits", lambda *a: 3)
         batch = 4
+    else:
+        monkeypatch.setattr(ops, "FOLD_MAX_ROWS", 16)
+        if route == "folded slices":
+            monkeypatch.setattr(ops, "skinny_splits", lambda blocks, K: 3)
+        batch = 5 if route == "folded" else 11
+        folded = []
+        inner = ops._skinny
+
+        def watched(a, w, n_out, gate_up, out_float32, norm=None, add_to=None):
+            folded.append((norm is not None and len(norm) == 3, add_to is not None))
+            return inner(a, w, n_out, gate_up, out_float32, norm, add_to)
+        monkeypatch.setattr(ops, "_skinny", watched)
     folder, dtype = tiny_folders["M"], "bfloat16"
     lengths = (5, 150, 77, 1, 64, 65, 33, 90, 129, 12, 70, 200, 3)
     seqs = random_tokens(TINY["M"]["vocab_size"], lengths, seed=19)
@@ -80,3 +93,5 @@ def test_other_kernel_routes_through_the_whole_engine(tiny_folders, monkeypatch,
     assert_close(run_ragged_batches(sess, seqs, batch_size=batch, poison=True), ref, dtype, f"ragged batches, route {route}")
     assert ops.launches > before
     assert sess.cache.slots.n_held == 0
+    if route.startswith("folded"):   # norms were read from the statistics that the sums left, and sums were taken
+        assert (True, False) in folded and (False, True) in folded

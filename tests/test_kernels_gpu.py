@@ -339,6 +339,71 @@ def test_skinny_product_variants(ops, ref, M, splits, tiled, warps):
         ops.force_skinny = None
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 11, 16])
+@pytest.mark.parametrize("splits,tiled,warps", [(1, False, 8), (1, True, 4), (3, True, 8), (2, False, 4), (11, True, 4)])
+def test_skinny_product_with_norm_and_sum_inside(ops, ref, M, splits, tiled, warps):
+    """The decode product with the RMSNorm of its rows in the prologue and the residual sum in the epilogue, against
+    the norm kernel followed by the plain product and a 32-bit sum.  Rows have very different sizes, so that a row
+    normed with another row's statistics would show; the widths are no multiples of the kernel's tiles."""
+    dtype = torch.bfloat16
+    K, N = 1000, 328
+    try:
+        ops.force_skinny = (splits, tiled, warps)
+        x = rand((M, K), dtype, 90) * torch.logspace(-2, 2, M).cuda().to(dtype)[:, None]
+        gamma = (1.0 + rand((K,), dtype, 91, 0.3).float()).to(dtype)
+        w, w_pairs = rand((N, K), dtype, 92, 0.05), rand((2 * N, K), dtype, 93, 0.05)
+        if tiled:
+            ops.prepare_matrix(w)
+            ops.prepare_matrix(w_pairs, halves=2)
+        eps = 1e-5
+        normed = ops.rmsnorm(x, gamma, eps)
+        close(normed, ref.rmsnorm(x, gamma, eps), dtype, "norm kernel")
+        # the norm inside: the same bits as norm kernel + product almost everywhere (the statistics are summed in
+        # another order, which can move a rounding), and close to the restatement
+        want = ops._skinny(normed, w, N, False, False)
+        got = ops._skinny(x, w, N, False, False, norm=(gamma, eps))
+        close(got, ref.linear(ref.rmsnorm(x, gamma, eps), w), dtype, "product of the norm")
+        assert float((got == want).float().mean()) >= 0.99
+        want_act = ops._skinny(normed, w_pairs, N, True, False)
+        got_act = ops._skinny(x, w_pairs, N, True, False, norm=(gamma, eps))
+        close(got_act, ref.linear_swiglu(ref.rmsnorm(x, gamma, eps), w_pairs), dtype, "swiglu of the product of the norm")
+        assert float((got_act == want_act).float().mean()) >= 0.99
+        # the sum inside: exactly the 32-bit sum of the residual and the rounded product, rounded once
+        a = rand((M, K), dtype, 94)
+        w_back = rand((K, K), dtype, 95, 0.05)
+        if tiled:
+            ops.prepare_matrix(w_back)
+        residual = rand((M, K), dtype, 96, 2.0)
+        product = ops._skinny(a, w_back, K, False, False)
+        summed = residual.clone()
+        assert ops._skinny(a, w_back, K, False, False, add_to=summed) is summed
+        assert torch.equal(summed, (residual.float() + product.float()).to(dtype))
+        # both at once, as a layer's branch uses them
+        both = residual[:, :N].clone()
+        ops._skinny(x, w, N, False, False, norm=(gamma, eps), add_to=both)
+        assert torch.equal(both, (residual[:, :N].float() + got.float()).to(dtype))
+        # the statistics that the sum leaves for the next product's norm: the squares of the new rows, 16 columns a
+        # piece; a product that reads them gives what a product that reads the rows gives
+        from types import SimpleNamespace
+        stream = SimpleNamespace(x=residual.clone(), stats=None)
+        ops._skinny(a, w_back, K, False, False, add_to=stream)
+        assert torch.equal(stream.x, summed) and tuple(stream.stats.shape) == (M, -(-K // 16))
+        pieces = torch.nn.functional.pad(summed.float() ** 2, (0, -K % 16)).view(M, -1, 16).sum(-1)
+        assert torch.allclose(stream.stats, pieces, rtol=1e-5, atol=0)
+        with_stats = ops._skinny(summed, w, N, False, False, norm=(gamma, eps, stream.stats))
+        without = ops._skinny(summed, w, N, False, False, norm=(gamma, eps))
+        close(with_stats, ref.linear(ref.rmsnorm(summed, gamma, eps), w), dtype, "product of the norm from statistics")
+        assert float((with_stats == without).float().mean()) >= 0.99
+    finally:
+        ops.force_skinny = None
+    with pytest.raises(Exception, match="16 rows"):
+        ops._skinny(rand((17, K), dtype, 97), w, N, False, False, norm=(gamma, eps))
+    with pytest.raises(Exception, match="bfloat16"):
+        ops._skinny(x, w, N, False, False, norm=(gamma.float(), eps))
+    with pytest.raises(Exception, match="adds to"):
+        ops._skinny(x, w, N, False, False, add_to=residual)
+
+
 @pytest.mark.parametrize("heads,kv_heads,head_dim,window", [(8, 2, 128, None), (3, 1, 64, 150)])
 def test_prefill_attention_over_many_pages(ops, ref, heads, kv_heads, head_dim, window):
     """Long pieces appended to contexts that already hold tokens; one far key is made to stand out."""
