@@ -33,7 +33,7 @@
 #define PT_ROWS 128
 #define PT_D 128
 #define PT_IDS 128
-#define PT_THREADS 160   // four warps of rows and the issuer's warp
+#define PT_THREADS 192   // four warps of rows, the warp of the thread that issues the products and that of the thread that issues the copies
 
 #ifdef SB_TIMELINE
 // Tuning builds only: clock stamps of one block's issuer and of its first row, per page: [page][8].
@@ -154,41 +154,34 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     constexpr uint32_t O_COL = 2 * SB_PAGE;        // tensor memory: S buffers at columns 0 and 64, O from 128
 
     if (!owns_row) {
-        // ---- the issuer: one thread.  Page i lives in stage i & 1; a barrier of index i & 1 is in phase (i >> 1) & 1
-        // when page i's event completes.
+        // ---- two threads of two further warps.  One issues the products, the other the copies; each has only its own
+        // waits in its loop (one thread doing both needed ~2,500 clocks a page for its ~500 instructions and a dozen
+        // barrier look-ups, and the rows waited for it).  Page i lives in stage i & 1; a barrier of index i & 1 is in
+        // phase (i >> 1) & 1 when page i's event completes.
         if (tid == PT_ROWS) {
-            auto issue_k = [&](int i) {
-                const int y = (s_pages[i & (PT_IDS - 1)] * kv.n_kv_heads + kvh) * SB_PAGE;
-                mbar_expect_tx(&k_full[i & 1], STAGE);
-                tma_load_2d(k_s + (i & 1) * STAGE, &map_k, 0, y, &k_full[i & 1]);
-                tma_load_2d(k_s + (i & 1) * STAGE + KV_ATOM, &map_k, 64, y, &k_full[i & 1]);
-            };
-            auto issue_v = [&](int i) {
-                const int y = (s_pages[i & (PT_IDS - 1)] * kv.n_kv_heads + kvh) * SB_PAGE;
-                mbar_expect_tx(&v_full[i & 1], STAGE);
-                tma_load_2d(v_s + (i & 1) * STAGE, &map_v, 0, y, &v_full[i & 1]);
-                tma_load_2d(v_s + (i & 1) * STAGE + KV_ATOM, &map_v, 64, y, &v_full[i & 1]);
-            };
+            // The descriptors of every operand, once: Q (8 steps of 16 columns), K and V of both stages.
+            uint64_t q_desc[PT_D / 16], k_desc[2][PT_D / 16], v_desc[2][SB_PAGE / 16];
+#pragma unroll
+            for (int ks = 0; ks < PT_D / 16; ++ks) {
+                q_desc[ks] = desc_k_major(q_s + (ks >> 2) * Q_ATOM) + 2 * (ks & 3);
+#pragma unroll
+                for (int st = 0; st < 2; ++st) k_desc[st][ks] = desc_k_major(k_s + st * STAGE + (ks >> 2) * KV_ATOM) + 2 * (ks & 3);
+            }
+#pragma unroll
+            for (int ks = 0; ks < SB_PAGE / 16; ++ks)   // 16 keys per step: two groups of eight key rows of V
+#pragma unroll
+                for (int st = 0; st < 2; ++st) v_desc[st][ks] = desc_mn_major(v_s + st * STAGE + ks * 2048, KV_ATOM);
             auto issue_s = [&](int i) {   // S of page i into S buffer i & 1
                 mbar_wait(&k_full[i & 1], (i >> 1) & 1, abort_flag, status);
                 tc_fence_after();
-                const unsigned char* kt = k_s + (i & 1) * STAGE;
 #pragma unroll
                 for (int ks = 0; ks < PT_D / 16; ++ks)
-                    tc_mma(tmem + (i & 1) * SB_PAGE, desc_k_major(q_s + (ks >> 2) * Q_ATOM) + 2 * (ks & 3),
-                           desc_k_major(kt + (ks >> 2) * KV_ATOM) + 2 * (ks & 3), idesc_s, ks > 0 ? 1u : 0u);
+                    tc_mma(tmem + (i & 1) * SB_PAGE, q_desc[ks], (i & 1) ? k_desc[1][ks] : k_desc[0][ks], idesc_s, ks > 0 ? 1u : 0u);
                 tc_commit(&s_done[i & 1]);
             };
-            issue_s(0);   // keys of pages 0 and 1 and values of page 0 were asked for at the block's start
+            issue_s(0);
             for (int i = 0; i < n_pages && !*abort_flag; ++i) {
                 const int b = i & 1;
-                // Keys two pages ahead go into the stage of page i, once S of page i has read it.  That product was
-                // issued an iteration ago, so the wait is over; the copy is asked for before the next product is issued,
-                // because issuing blocks for as long as the tensor core works on the block's earlier products.
-                if (i + 2 < n_pages) {
-                    mbar_wait(&s_done[b], (i >> 1) & 1, abort_flag, status);
-                    issue_k(i + 2);
-                }
                 // S of the next page: its buffer was read by the rows in iteration i - 1 (p_ready of i - 1, waited for
                 // below), and the product that read P from it was issued before this one.
                 if (i + 1 < n_pages) issue_s(i + 1);
@@ -198,16 +191,31 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 mbar_wait(&v_full[b], (i >> 1) & 1, abort_flag, status);
                 if (*abort_flag) break;
                 tc_fence_after();
-                const unsigned char* vt = v_s + b * STAGE;
 #pragma unroll
-                for (int ks = 0; ks < SB_PAGE / 16; ++ks)   // 16 keys per step: 32 bytes along P's rows, two groups of eight key rows of V
-                    tc_mma_ts(tmem + O_COL, tmem + b * SB_PAGE + 8 * ks, desc_mn_major(vt + ks * 2048, KV_ATOM), idesc_o,
+                for (int ks = 0; ks < SB_PAGE / 16; ++ks)   // 16 keys per step: 32 bytes = 8 columns along P's rows
+                    tc_mma_ts(tmem + O_COL, tmem + b * SB_PAGE + 8 * ks, b ? v_desc[1][ks] : v_desc[0][ks], idesc_o,
                               (i > 0 || ks > 0) ? 1u : 0u);
                 tc_commit(&o_done[b]);
                 PT_STAMP(i, 2);
+            }
+        } else if (tid == PT_ROWS + 32) {
+            // The copies.  Keys of pages 0 and 1 and values of page 0 were asked for at the block's start.
+            auto issue_kv = [&](int i, unsigned char* base, const CUtensorMap* map, uint64_t* bar) {
+                const int y = (s_pages[i & (PT_IDS - 1)] * kv.n_kv_heads + kvh) * SB_PAGE;
+                mbar_expect_tx(bar, STAGE);
+                tma_load_2d(base + (i & 1) * STAGE, map, 0, y, bar);
+                tma_load_2d(base + (i & 1) * STAGE + KV_ATOM, map, 64, y, bar);
+            };
+            for (int i = 0; i < n_pages && !*abort_flag; ++i) {
                 if (i + 1 < n_pages) {   // values of the next page go into the stage of page i - 1, once its product is done
                     if (i > 0) mbar_wait(&o_done[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag, status);
-                    issue_v(i + 1);
+                    if (*abort_flag) break;
+                    issue_kv(i + 1, v_s, &map_v, &v_full[(i + 1) & 1]);
+                }
+                if (i + 2 < n_pages) {   // keys two pages ahead go into the stage of page i, once S of page i has read it
+                    mbar_wait(&s_done[i & 1], (i >> 1) & 1, abort_flag, status);
+                    if (*abort_flag) break;
+                    issue_kv(i + 2, k_s, &map_k, &k_full[i & 1]);
                 }
             }
             if (*abort_flag) {   // leaving early: give the copies in flight a bounded time to land

@@ -135,6 +135,15 @@ __device__ __forceinline__ void tc_st32_u32(uint32_t taddr, const uint32_t* v) {
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
 
+// 16 columns of raw 32-bit words into tensor memory.
+__device__ __forceinline__ void tc_st16_u32(uint32_t taddr, const uint32_t* v) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]), "r"(v[9]),
+                   "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15])
+                 : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
 // Shared-memory descriptors (sm_100 version, 128-byte swizzle).
 // K-major tile [rows][64 elements] as TMA writes it: rows 128 bytes apart, groups of eight rows 1024 bytes apart.
 __device__ __forceinline__ uint64_t desc_k_major(const void* tile) {
