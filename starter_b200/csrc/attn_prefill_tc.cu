@@ -8,22 +8,32 @@
 // Layout of the work.  As in attn_prefill.cu the query rows of one sequence and one key/value head are
 // the pairs (new position, query head of the group), position-major; a block takes 128 of them, one per
 // thread and per lane of tensor memory.  Per key page (64 keys, one cache page):
-//   thread 0 issues  S[128 x 64] = Q[128 x 128] K^T          (8 tcgen05.mma of K = 16, both operands K-major)
-//   every thread reads its row of S from tensor memory, masks, updates its running maximum and sum,
+//   a thread issues  S[128 x 64] = Q[128 x 128] K^T          (8 tcgen05.mma of K = 16, both operands K-major)
+//   every row thread reads its row of S from tensor memory, masks, updates its running maximum and sum,
 //   and writes its row of P (bfloat16) back into tensor memory, over the first half of the S it read
-//   thread 0 issues  O_page[128 x 128] = P[128 x 64] V       (4 tcgen05.mma with P read from tensor memory; V as
+//   the thread issues  O[128 x 128] += P[128 x 64] V         (4 tcgen05.mma with P read from tensor memory; V as
 //                                                             it lies in the cache, [key][d], is the MN-major form)
-//   every thread reads its row of O_page and folds it into its 128 accumulators: acc = acc * alpha + O_page.
-// Who does what.  Warps 0-3 own the rows (softmax).  One thread of a fifth warp issues every TMA copy and every
-// tcgen05.mma and nothing else: issuing a product takes about as long as the tensor core needs for it (measured:
-// 840 cycles for S, 820 for O += P V), and a thread that also owned a row made its whole block wait for that.
-// The products run ahead of the softmax: S of page i + 1 goes into the second of two S buffers in tensor memory
-// while the rows work on page i, and O += P V of page i runs while they start on page i + 1.  Keys arrive two
-// pages ahead and values one page ahead, in two stages each.  The rows and the issuer meet only through
-// mbarriers (S ready, O done, P written); there is no block-wide barrier inside the loop.  Two blocks share an SM
-// (97 KB of shared memory and 256 columns of tensor memory each).  Every wait on an mbarrier is bounded; on a time-out the block raises
-// SB_STATUS_TIMEOUT and a flag in shared memory that ends every other wait of the block, which then frees its
-// tensor memory and returns.
+//   O stays in tensor memory across the pages; the rows rescale it only when their reference maximum moves.
+// Who does what.  Warps 0-3 own the rows (softmax).  One thread of a fifth warp issues every tcgen05.mma, one thread
+// of a sixth warp every TMA copy, and neither does anything else.  (A thread that also owned a row made its whole
+// block wait; one thread issuing both products and copies needed ~2,500 clocks a page for its ~500 instructions and
+// dozen barrier look-ups, and the rows waited for it: 612 -> 503 us at 8,192 tokens when the two were parted and the
+// operand descriptors computed once.)  The products run ahead of the softmax: S of page i + 1 goes into the second of
+// two S buffers in tensor memory while the rows work on page i, and O += P V of page i runs while they start on
+// page i + 1.  Keys arrive two pages ahead and values one page ahead, in two stages each.  Rows, products and copies
+// meet only through mbarriers (keys landed, values landed, S ready, O done, P written); there is no block-wide
+// barrier inside the loop.  Two blocks share an SM (97 KB of shared memory and 256 columns of tensor memory each).
+// Measured on a B200, and what it means for this kernel: the tensor core takes 48 clocks for a product of N = 64
+// and 64 for N = 128 (K = 16), whether operand A comes from shared or tensor memory and however the products
+// depend on one another, but a group of products that ends in a commit costs 250-450 clocks more when the block
+// has nothing else queued (two blocks fill one another's gaps: together 620 clocks a page); the exp2 unit takes
+// 8 clocks per warp instruction, so a page's 64 exponentials per row cost 512 clocks per warp, 587 when two warps
+// share a scheduler, 800 for a warp alone.  With two blocks per SM a page per block takes ~1,900 clocks: ~1,150
+// for the exponentials of both blocks' rows (they share the exp2 unit) and ~700 for the trips to tensor memory and
+// the barriers around them.  Exponentials on the FMA units (a cubic) were measured and are slower at two warps per
+// scheduler; so were two threads per row, and the read of the next S overlapped with the write of P.
+// Every wait on an mbarrier is bounded; on a time-out the block raises SB_STATUS_TIMEOUT and a flag in shared
+// memory that ends every other wait of the block, which then frees its tensor memory and returns.
 #include <cuda.h>
 
 #include <mutex>
