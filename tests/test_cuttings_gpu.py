@@ -52,11 +52,11 @@ def test_dependent_launch_changes_no_bit(tiny_folders, dtype):
     assert_close(got[True][:3], plain_logits(folder, seqs, dtype), dtype, "dependent launch")
 
 
-@pytest.mark.parametrize("route", ["stream", "balanced", "slices", "folded", "folded slices"])
+@pytest.mark.parametrize("route", ["stream", "balanced", "balanced fused", "slices", "folded", "folded slices"])
 def test_other_kernel_routes_through_the_whole_engine(tiny_folders, monkeypatch, route):
     """The shape rules send the test configurations to a few of the kernels only.  Here the rules are bent so
     that the whole engine runs on the others: the TMA + tcgen05 product for every matrix (batches of 12), the
-    balanced decode attention (with the separate q/k kernel before it), and K slices / key splits that meet in
+    balanced decode attention (with the q/k preparation as a kernel of its own, the default, and inside it), and K slices / key splits that meet in
     clusters; and the decode products that take the norm before them and the residual sum after them into
     themselves (off by default: slower than the norm kernel as measured).  Freed pages are poisoned between batches."""
     from starter_b200.csrc.ops import get_ops
@@ -65,8 +65,9 @@ def test_other_kernel_routes_through_the_whole_engine(tiny_folders, monkeypatch,
         monkeypatch.setattr(ops, "STREAM_MIN_WORK", 0)
         monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 0)
         batch = 12
-    elif route == "balanced":
+    elif route.startswith("balanced"):
         monkeypatch.setattr(ops, "decode_resident", lambda *a: 0)
+        monkeypatch.setattr(ops, "fuse_qk_balanced", route == "balanced fused")
         batch = 5
     elif route == "slices":
         monkeypatch.setattr(ops, "skinny_splits", lambda blocks, K: 3)

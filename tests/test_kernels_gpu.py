@@ -270,6 +270,7 @@ def test_decode_attention_with_preparation_inside(ops, ref, monkeypatch, heads, 
     dtype = torch.bfloat16
     if splits is None:   # the balanced kernel (equal shares of all pages per block), with the preparation inside as well
         monkeypatch.setattr(ops, "decode_resident", lambda *a: 0)
+        monkeypatch.setattr(ops, "fuse_qk_balanced", True)   # off by default: slower in the step than a kernel of its own
     else:
         monkeypatch.setattr(ops, "decode_balanced", False)
         monkeypatch.setattr(ops, "decode_splits", lambda *a: splits)
