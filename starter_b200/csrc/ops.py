@@ -237,7 +237,7 @@ class Ops:
     # registers and loses (4B sizes at batch 32: 6.64 against 5.35 ms).
     SKINNY_MAX_ROWS = int(os.environ.get("STARTER_B200_SKINNY_MAX_ROWS", 16))
     STREAM_MIN_ROWS = 9   # the TMA + tcgen05 product serves the output head from here on
-    STREAM_MAX_ROWS = 64
+    STREAM_MAX_ROWS = 32   # 778 MB head, us by rows (this kernel / cuBLAS): 16: 126 / 132, 32: 130 / 134, 48: 137 / 131, 64: 138 / 133
     STREAM_MIN_WORK = int(os.environ.get("STARTER_B200_STREAM_MIN", 300_000_000))  # elements of W below which the simpler kernels do as well
 
     def kernel_status(self, device) -> torch.Tensor:
@@ -290,7 +290,7 @@ class Ops:
         """Measured on a B200 (microbench.py): per launch the TMA-fed kernel pays about 9 us before and
         after it streams (set-up, first data, the pass through scratch for shared tiles) and then streams
         at 6.3-6.9 TB/s; the warp-level kernel pays about 3 us and streams at 4.7 TB/s, more on very large
-        matrices.  So: the output head for 9 to 64 rows, nothing smaller."""
+        matrices.  So: the output head for 9 to 32 rows, nothing smaller; from 33 rows on cuBLAS is ahead there too."""
         return (self.use_stream and self.STREAM_MIN_ROWS <= M <= (32 if gate_up else self.STREAM_MAX_ROWS)
                 and K % 8 == 0 and K >= 64 and n_out * K * (2 if gate_up else 1) >= self.STREAM_MIN_WORK)
 
