@@ -117,7 +117,7 @@ class KVGroup:
         if self._dirty:
             rows = torch.tensor(sorted(self._dirty), dtype=torch.int32)
             idx, data = staging.upload([rows, self.table_host[rows.long()]])
-            self.table.index_copy_(0, idx.long(), data)
+            self.table[idx] = data
             self._dirty.clear()
 
     def capacity_tokens(self) -> int:
@@ -267,7 +267,7 @@ class Cache:
             rows = sorted(self._dirty_lengths)
             idx, vals = self.staging.upload([torch.tensor(rows, dtype=torch.int32),
                                              torch.tensor([self.lengths_host[r] for r in rows], dtype=torch.int32)])
-            self.lengths.index_copy_(0, idx.long(), vals)
+            self.lengths[idx] = vals
             self._dirty_lengths.clear()
 
     # ---- accounting --------------------------------------------------------------------

@@ -82,12 +82,17 @@ class Stepper:
         slot slots[b]; everything goes up in one copy."""
         cache = self.cache
         B = len(slots)
-        lens = torch.as_tensor(list(q_lens), dtype=torch.int32)
-        cu = torch.zeros(B + 1, dtype=torch.int32)
-        torch.cumsum(lens, 0, out=cu[1:])
-        M = int(cu[-1])
-        row_seq = torch.repeat_interleave(torch.arange(B, dtype=torch.int32), lens.long(), output_size=M)
-        seq_slot, cu_q, row_seq, *rest = self.staging.upload([torch.as_tensor(list(slots), dtype=torch.int32), cu, row_seq, *tail])
+        cu = [0]
+        for n in q_lens:
+            cu.append(cu[-1] + int(n))
+        M = cu[-1]
+        head = torch.frombuffer(array.array("i", [*slots, *cu]), dtype=torch.int32)   # the short arrays in one piece
+        if B == 1:
+            row_seq = torch.zeros(M, dtype=torch.int32)
+        else:
+            row_seq = torch.repeat_interleave(torch.arange(B, dtype=torch.int32), torch.as_tensor(list(q_lens)), output_size=M)
+        head, row_seq, *rest = self.staging.upload([head, row_seq, *tail])
+        seq_slot, cu_q = head[:B], head[B:]
         kv_bound = max(cache.lengths_host[s] + n for s, n in zip(slots, q_lens))
         ctx = StepContext(
             runtime=self.runtime, cache=cache, n_seqs=B, n_rows=M, max_q_len=max(q_lens), kv_bound=kv_bound,
