@@ -135,3 +135,31 @@ def test_random_traffic_keeps_the_books():
         cache.free(s)
     cache.check()
     assert all(g.pages.n_held == 0 for g in cache.groups)
+
+
+def test_staging_keeps_what_it_was_given_and_the_step_reads_token_lists():
+    """The host-to-device staging lays the parts side by side and hands back views in their shapes and order; what
+    goes up is what the tensors held at the call, whatever the host writes to them afterwards.  (On the CPU the
+    "device" is the host: the parts are copied.)  Token ids given as lists, tuples, tensors or other integers all
+    become the same int32 tensor."""
+    from starter_b200.cache.staging import HostStaging
+    from starter_b200.engine.step import _int32_tensor
+
+    staging = HostStaging("cpu")
+    a = torch.tensor([3, 1, 2], dtype=torch.int32)
+    b = torch.arange(6, dtype=torch.int32).view(2, 3)
+    empty = torch.empty(0, dtype=torch.int32)
+    got_a, got_empty, got_b = staging.upload([a, empty, b])
+    a[0] = 99
+    b[1, 2] = 99
+    assert got_a.tolist() == [3, 1, 2] and got_b.tolist() == [[0, 1, 2], [3, 4, 5]] and got_empty.numel() == 0
+    assert staging.upload([]) == []
+
+    import numpy as np
+    want = [5, 0, 151935]
+    for given in (want, tuple(want), torch.tensor(want), torch.tensor(want, dtype=torch.int64), np.array(want),
+                  [np.int64(v) for v in want], []):
+        out = _int32_tensor(given)
+        assert out.dtype == torch.int32 and out.dim() == 1 and out.tolist() == (want if len(given) else [])
+    with pytest.raises(Exception):
+        _int32_tensor([1, "two"])
