@@ -509,6 +509,9 @@ def run_reference(args, raw, workload) -> int:
                     torch.cuda.synchronize()
                     ms = replay_decode(eng, (b, short), context - steps - warmup, steps)
                     points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+                    half = context // 2   # the same plan at half the context, as this library's arm measures it
+                    ms = replay_decode(eng, (b, short), half - steps // 2 - warmup, steps)
+                    points[f"decode_b{b}_ctx{half}"] = round(b * 1000.0 / ms, 1)
             del eng
 
             def prefill_ms_of(n_tokens, repeats):

@@ -115,6 +115,7 @@ class Ops:
         self._kernel_status = None
         self._status_override = None
         self.decode_balanced = os.environ.get("STARTER_B200_ATTN", "balanced") != "split"
+        self.force_decode_route = None   # "split" or "balanced" for tests; None = the rule in _decode_route
         self.fuse_qk = os.environ.get("STARTER_B200_FUSE_QK", "1") != "0"
         # With the balanced kernel (more pairs than blocks fit at once) the preparation stays a kernel of its own: a block
         # walks several (sequence, kv head) pairs one after another and pays each pair's preparation on its own path.
@@ -500,15 +501,25 @@ class Ops:
 
     def _decode_route(self, ctx, kv, n_heads):
         """Which decode kernel serves a step of one token per sequence (bfloat16 cache with head size 64 or 128, at most
-        16 query heads per kv head): "split" (a grid of (sequence, kv head, split)) or, when there are more (sequence,
-        kv head) pairs than blocks fit at once, "balanced" (one block per SM, equal shares of all pages); None when the
-        step is of another kind."""
+        16 query heads per kv head): "split" (a grid of (sequence, kv head, split), the blocks handed out by the
+        hardware as others end) or "balanced" (one block per SM, equal shares of all pages, worked out on the device
+        from the lengths); None when the step is of another kind.
+
+        Measured alone at 4B sizes with sequences of equal length (us, balanced / split with one block per pair):
+        batch 64 at context 2,048: 95.8 / 87.9, at 4,096: 168.3 / 163.8; batch 128 at 2,048: 175 / 169; batch 256 at 1,024:
+        191 / 173; in the step at batch 64: 8.50 / 8.36 ms.  The balanced kernel pays ~6 us before its first page and its
+        blocks end up to 10 us apart; blocks handed out one by one even that out by themselves.  With very unequal
+        lengths (``ctx.uneven``: the longest sequence more than three times the mean) a block per pair would leave the
+        longest to one block, and the balanced kernel takes over where the pairs outnumber the blocks that fit."""
         if kv.head_dim not in (64, 128) or n_heads % kv.n_kv_heads or n_heads // kv.n_kv_heads > 16:
             return None
         if not (ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs):
             return None
+        if self.force_decode_route is not None:
+            return self.force_decode_route
         pairs = ctx.n_seqs * kv.n_kv_heads
-        if self.decode_balanced and pairs > self.decode_resident(kv.head_dim) and ctx.n_seqs <= 1024:
+        if (self.decode_balanced and getattr(ctx, "uneven", False) and pairs > self.decode_resident(kv.head_dim)
+                and ctx.n_seqs <= 1024):
             return "balanced"
         return "split"
 

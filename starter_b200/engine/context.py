@@ -14,7 +14,7 @@ ragged batch, described once on the device and read by every kernel:
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict
+from typing import Any, Dict, Sequence
 
 import torch
 
@@ -46,6 +46,7 @@ class StepContext:
     lengths: torch.Tensor   # int32 [n_slots + 1], the cache's
     status: torch.Tensor    # int32 [1], kernels raise bits here instead of faulting
     scratch: Dict[str, Any] = field(default_factory=dict)
+    uneven: bool = False    # host-side hint: the longest sequence is several times the mean (see lengths_uneven)
 
     @property
     def ops(self):
@@ -54,6 +55,16 @@ class StepContext:
     @property
     def is_decode(self) -> bool:
         return self.max_q_len == 1
+
+
+def lengths_uneven(lengths: Sequence[int], page: int = 64) -> bool:
+    """Whether a batch's sequences are of very unequal length: the longest holds more than three times the mean
+    number of cache pages.  Kernels that hand each sequence's keys to a block of its own then wait for the longest
+    one, and one that shares all pages out evenly is the better choice (the call table decides)."""
+    if len(lengths) < 2:
+        return False
+    pages = [int(n) // page + 1 for n in lengths]
+    return max(pages) * len(pages) > 3 * sum(pages)
 
 
 class ResidualStream:

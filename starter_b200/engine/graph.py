@@ -29,7 +29,7 @@ from typing import Iterator, List, Optional, Sequence
 import torch
 
 from ..sampling.sampler import SamplingParams, select
-from .context import StepContext
+from .context import StepContext, lengths_uneven
 from .step import raise_status_bits
 
 
@@ -43,10 +43,11 @@ def bucket_size(n: int) -> int:
 class _Bucket:
     """Device buffers and the captured graph of one batch size."""
 
-    def __init__(self, session, size: int, greedy: bool):
+    def __init__(self, session, size: int, greedy: bool, uneven: bool = False):
         self.session = session
         self.size = size
         self.greedy = greedy
+        self.uneven = uneven     # captured for batches of very unequal lengths (the kernels may be others)
         dev = session.device
         cache = session.cache
         i32 = dict(dtype=torch.int32, device=dev)
@@ -62,7 +63,7 @@ class _Bucket:
         self.ctx = StepContext(
             runtime=session.runtime, cache=cache, n_seqs=size, n_rows=size, max_q_len=1,
             kv_bound=cache.max_seq_tokens, seq_slot=self.seq_slot, cu_q=self.cu_q, row_seq=self.row_seq,
-            lengths=cache.lengths, status=self.status)
+            lengths=cache.lengths, status=self.status, uneven=uneven)
         self.graph: Optional[torch.cuda.CUDAGraph] = None
 
     def body(self) -> None:
@@ -142,15 +143,17 @@ class GraphDecoder:
         self.buckets = {}
         self.history: List[List[int]] = []
 
-    def new_bucket(self, n: int) -> _Bucket:
+    def new_bucket(self, n: int, uneven: bool = False) -> _Bucket:
         """Buffers for ``n`` sequences with every row on the null slot, nothing captured."""
-        return _Bucket(self.session, bucket_size(n), self.greedy)
+        return _Bucket(self.session, bucket_size(n), self.greedy, uneven)
 
-    def bucket(self, n: int) -> _Bucket:
+    def bucket(self, n: int, uneven: bool = False) -> _Bucket:
+        """The captured graph for ``n`` sequences; one more per size for batches of very unequal lengths, captured
+        when the first such batch comes."""
         size = bucket_size(n)
-        b = self.buckets.get(size)
+        b = self.buckets.get((size, uneven))
         if b is None:
-            b = self.buckets[size] = self.new_bucket(size)
+            b = self.buckets[(size, uneven)] = self.new_bucket(size, uneven)
             b.capture()
         return b
 
@@ -183,7 +186,7 @@ class GraphDecoder:
         n = len(slots)
         done_steps = 0
         while live and done_steps < n_steps:
-            b = self.bucket(len(live))
+            b = self.bucket(len(live), lengths_uneven([cache.lengths_host[slots[i]] + 1 for i in live]))
             cache.flush()
             b.load([slots[i] for i in live], [last[i] for i in live], [request_ids[i] for i in live],
                    first_step + done_steps, sampling)

@@ -20,7 +20,7 @@ from typing import List, Optional, Sequence
 import torch
 
 from ..cache.cache import Cache
-from .context import StepContext
+from .context import StepContext, lengths_uneven
 
 STATUS_BAD_TOKEN = 1
 STATUS_NO_PAGE = 2
@@ -97,6 +97,7 @@ class Stepper:
         ctx = StepContext(
             runtime=self.runtime, cache=cache, n_seqs=B, n_rows=M, max_q_len=max(q_lens), kv_bound=kv_bound,
             seq_slot=seq_slot, cu_q=cu_q, row_seq=row_seq, lengths=cache.lengths, status=self.status,
+            uneven=lengths_uneven([cache.lengths_host[s] + n for s, n in zip(slots, q_lens)]),
         )
         return ctx, rest
 

@@ -66,7 +66,7 @@ def test_other_kernel_routes_through_the_whole_engine(tiny_folders, monkeypatch,
         monkeypatch.setattr(ops, "SKINNY_MAX_ROWS", 0)
         batch = 12
     elif route.startswith("balanced"):
-        monkeypatch.setattr(ops, "decode_resident", lambda *a: 0)
+        monkeypatch.setattr(ops, "force_decode_route", "balanced")
         monkeypatch.setattr(ops, "fuse_qk_balanced", route == "balanced fused")
         batch = 5
     elif route == "slices":

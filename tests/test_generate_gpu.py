@@ -150,7 +150,7 @@ def test_a_new_seed_replays_the_same_graphs(tiny_folders):
         assert outs[-1] == eager.generate_all(prompts, 10, temperature=temperature, top_k=top_k, seed=seed)
     assert outs[0] == outs[3] and outs[0] != outs[1]
     assert set(eng.generator._decoders) == {False}           # one decoder for every sampled run
-    assert list(eng.generator._decoders[False].buckets) == [4]
+    assert list(eng.generator._decoders[False].buckets) == [(4, False)]   # (sequences, very unequal lengths)
     eng.generate_all(prompts, 4)
     assert set(eng.generator._decoders) == {False, True}
 
@@ -186,3 +186,29 @@ def test_a_captured_step_brings_its_status_with_its_tokens(tiny_folders):
     sess.cache.reserve(slot, 16)
     assert len(list(decoder.run([slot], [7], [0], 1, 4))) == 4
     sess.cache.free(slot)
+
+
+def test_batches_of_very_unequal_lengths_take_the_kernel_that_shares_pages_out(tiny_folders, monkeypatch):
+    """Where the (sequence, kv head) pairs outnumber the blocks the GPU holds, a batch whose longest sequence is
+    several times the mean is served by the decode attention that shares all pages out evenly, in a graph of its
+    own; a batch of equal lengths keeps the kernel with a block per pair.  Both give the tokens of the plain
+    implementation."""
+    from starter_b200.csrc.ops import get_ops
+    from starter_b200.engine.context import lengths_uneven
+    assert lengths_uneven([900, 5, 7, 3, 9, 4, 6, 8]) and not lengths_uneven([100, 90, 120, 80]) and not lengths_uneven([500])
+    ops = get_ops(verbose=False)
+    monkeypatch.setattr(ops, "decode_resident", lambda *a: 4)    # so that eight sequences of two kv heads are "many"
+    monkeypatch.setattr(ops, "fuse_qk", False)
+    calls = []
+    inner = ops._balanced_scratch
+    monkeypatch.setattr(ops, "_balanced_scratch", lambda *a: (calls.append(1), inner(*a))[1])
+    folder = tiny_folders["M"]
+    cfg, tensors = plain.read_folder(folder)
+    eng = Engine(folder, dtype="bfloat16", max_batch=8, max_context=768)
+    for lengths, balanced in (((600, 5, 7, 3, 9, 4, 6, 8), True), ((40, 44, 38, 41, 39, 45, 42, 40), False)):
+        prompts = random_tokens(TINY["M"]["vocab_size"], lengths, seed=31)
+        calls.clear()
+        got = eng.generate_all(prompts, 6)
+        assert bool(calls) == balanced, f"lengths {lengths}: the balanced kernel ran {len(calls)} times"
+        tokens_agree(got, plain.generate(cfg, tensors, prompts, 6, "bfloat16"), cfg, tensors, prompts, "bfloat16", 2e-2)
+    assert eng.session.cache.slots.n_held == 0

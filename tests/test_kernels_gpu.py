@@ -221,7 +221,7 @@ def test_decode_attention(ops, ref, monkeypatch, heads, kv_heads, head_dim, wind
     in the longest sequence one far key is made to stand out."""
     dtype = torch.bfloat16
     if splits is None:   # the balanced kernel, whatever the number of pairs
-        monkeypatch.setattr(ops, "decode_resident", lambda *a: 0)
+        monkeypatch.setattr(ops, "force_decode_route", "balanced")
     else:                # the split-key kernel with a fixed number of splits
         monkeypatch.setattr(ops, "decode_balanced", False)
         monkeypatch.setattr(ops, "decode_splits", lambda *a: splits)
@@ -269,7 +269,7 @@ def test_decode_attention_with_preparation_inside(ops, ref, monkeypatch, heads, 
     the start of a page, at its end, and in a sequence's first position."""
     dtype = torch.bfloat16
     if splits is None:   # the balanced kernel (equal shares of all pages per block), with the preparation inside as well
-        monkeypatch.setattr(ops, "decode_resident", lambda *a: 0)
+        monkeypatch.setattr(ops, "force_decode_route", "balanced")
         monkeypatch.setattr(ops, "fuse_qk_balanced", True)   # off by default: slower in the step than a kernel of its own
     else:
         monkeypatch.setattr(ops, "decode_balanced", False)
