@@ -116,6 +116,7 @@ class Ops:
         self._status_override = None
         self.decode_balanced = os.environ.get("STARTER_B200_ATTN", "balanced") != "split"
         self.force_decode_route = None   # "split" or "balanced" for tests; None = the rule in _decode_route
+        self._most_kv_heads = 1          # the most kv heads a decode step has brought so far (for uneven_matters)
         self.fuse_qk = os.environ.get("STARTER_B200_FUSE_QK", "1") != "0"
         # With the balanced kernel (more pairs than blocks fit at once) the preparation stays a kernel of its own: a block
         # walks several (sequence, kv head) pairs one after another and pays each pair's preparation on its own path.
@@ -517,11 +518,19 @@ class Ops:
             return None
         if self.force_decode_route is not None:
             return self.force_decode_route
+        self._most_kv_heads = max(self._most_kv_heads, kv.n_kv_heads)
         pairs = ctx.n_seqs * kv.n_kv_heads
         if (self.decode_balanced and getattr(ctx, "uneven", False) and pairs > self.decode_resident(kv.head_dim)
                 and ctx.n_seqs <= 1024):
             return "balanced"
         return "split"
+
+    def uneven_matters(self, n_seqs: int) -> bool:
+        """Whether a decode step of this many sequences would run other kernels when its context says ``uneven``
+        (so that a caller who keeps captured graphs need not keep two alike)."""
+        if self.force_decode_route is not None or not self.decode_balanced:
+            return False
+        return n_seqs <= 1024 and n_seqs * self._most_kv_heads > self.decode_resident(128)
 
     def _split_decode(self, ctx, kv, n_heads) -> bool:
         return self._decode_route(ctx, kv, n_heads) == "split"

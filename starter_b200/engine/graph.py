@@ -186,7 +186,10 @@ class GraphDecoder:
         n = len(slots)
         done_steps = 0
         while live and done_steps < n_steps:
-            b = self.bucket(len(live), lengths_uneven([cache.lengths_host[slots[i]] + 1 for i in live]))
+            matters = getattr(sess.runtime.ops, "uneven_matters", None)
+            uneven = (lengths_uneven([cache.lengths_host[slots[i]] + 1 for i in live])
+                      and (matters is None or matters(bucket_size(len(live)))))
+            b = self.bucket(len(live), uneven)
             cache.flush()
             b.load([slots[i] for i in live], [last[i] for i in live], [request_ids[i] for i in live],
                    first_step + done_steps, sampling)

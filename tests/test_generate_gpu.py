@@ -212,3 +212,9 @@ def test_batches_of_very_unequal_lengths_take_the_kernel_that_shares_pages_out(t
         assert bool(calls) == balanced, f"lengths {lengths}: the balanced kernel ran {len(calls)} times"
         tokens_agree(got, plain.generate(cfg, tensors, prompts, 6, "bfloat16"), cfg, tensors, prompts, "bfloat16", 2e-2)
     assert eng.session.cache.slots.n_held == 0
+    assert set(eng.generator._decoder(SamplingParams()).buckets) == {(8, True), (8, False)}   # a graph for each kind of batch
+    # where the pairs are few the kernels are the same either way, and so is the graph
+    monkeypatch.undo()
+    small = Engine(folder, dtype="bfloat16", max_batch=8, max_context=768)
+    small.generate_all(random_tokens(TINY["M"]["vocab_size"], (600, 5, 7, 3, 9, 4, 6, 8), seed=31), 3)
+    assert set(small.generator._decoder(SamplingParams()).buckets) == {(8, False)}
