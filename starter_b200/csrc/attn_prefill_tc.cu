@@ -15,7 +15,11 @@
 //                                                             it lies in the cache, [key][d], is the MN-major form)
 //   O stays in tensor memory across the pages; the rows rescale it only when their reference maximum moves.
 // Who does what.  Warps 0-3 own the rows (softmax).  One thread of a fifth warp issues every tcgen05.mma, one thread
-// of a sixth warp every TMA copy, and neither does anything else.  (A thread that also owned a row made its whole
+// of a sixth warp every TMA copy, and neither does anything else; two more warps only make the second group of four
+// whole, so that it can hand registers to the first (setmaxnreg: the block starts with 128 a thread, the rows go on
+// with 216, the others with 40; measured on one box against 192 threads of 168 registers: 55.8 -> 52.9 us at 2,048
+// tokens, 155.8 -> 155.1 at 4,096, 505 -> 512 at 8,192: the short prompt, whose time is that of its longest blocks,
+// gains; the split of the registers itself does not matter, 168 / 192 / 216 for the rows give the same times).  (A thread that also owned a row made its whole
 // block wait; one thread issuing both products and copies needed ~2,500 clocks a page for its ~500 instructions and
 // dozen barrier look-ups, and the rows waited for it: 612 -> 503 us at 8,192 tokens when the two were parted and the
 // operand descriptors computed once.)  The products run ahead of the softmax: S of page i + 1 goes into the second of
@@ -43,7 +47,8 @@
 #define PT_ROWS 128
 #define PT_D 128
 #define PT_IDS 128
-#define PT_THREADS 192   // four warps of rows, the warp of the thread that issues the products and that of the thread that issues the copies
+#define PT_THREADS 256   // two groups of four warps: the rows; and the warp of the thread that issues the products, that of the thread that
+                         // issues the copies and two spare ones, which together hand most of their registers to the rows
 
 #ifdef SB_TIMELINE
 // Tuning builds only: clock stamps of one block's issuer and of its first row, per page: [page][8].
@@ -158,35 +163,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
+    // The rows hold a page's 64 scores and their packed probabilities in registers; the other warps need a few dozen.
+    // The block starts with 128 registers a thread and deals them out anew, each group at the head of its own branch;
+    // the branches do not meet again (code after a meeting would have to live with the smaller number).
     const uint32_t tmem = *tmem_slot;
     const uint32_t tmem_row = tmem + ((uint32_t)((warp & 3) * 32) << 16);   // this warp's 32 lanes
     const uint32_t idesc_s = umma_idesc(SB_PAGE, 0), idesc_o = umma_idesc(PT_D, 1);
     constexpr uint32_t O_COL = 2 * SB_PAGE;        // tensor memory: S buffers at columns 0 and 64, O from 128
 
     if (!owns_row) {
+        asm volatile("setmaxnreg.dec.sync.aligned.u32 40;" ::: "memory");
         // ---- two threads of two further warps.  One issues the products, the other the copies; each has only its own
         // waits in its loop (one thread doing both needed ~2,500 clocks a page for its ~500 instructions and a dozen
         // barrier look-ups, and the rows waited for it).  Page i lives in stage i & 1; a barrier of index i & 1 is in
         // phase (i >> 1) & 1 when page i's event completes.
         if (tid == PT_ROWS) {
-            // The descriptors of every operand, once: Q (8 steps of 16 columns), K and V of both stages.
-            uint64_t q_desc[PT_D / 16], k_desc[2][PT_D / 16], v_desc[2][SB_PAGE / 16];
-#pragma unroll
-            for (int ks = 0; ks < PT_D / 16; ++ks) {
-                q_desc[ks] = desc_k_major(q_s + (ks >> 2) * Q_ATOM) + 2 * (ks & 3);
-#pragma unroll
-                for (int st = 0; st < 2; ++st) k_desc[st][ks] = desc_k_major(k_s + st * STAGE + (ks >> 2) * KV_ATOM) + 2 * (ks & 3);
-            }
-#pragma unroll
-            for (int ks = 0; ks < SB_PAGE / 16; ++ks)   // 16 keys per step: two groups of eight key rows of V
-#pragma unroll
-                for (int st = 0; st < 2; ++st) v_desc[st][ks] = desc_mn_major(v_s + st * STAGE + ks * 2048, KV_ATOM);
+            // The descriptors of the operands: one each for Q and for K and V of both stages; a step of 16 columns (32
+            // bytes) or a further block of 64 columns adds a constant to the address field.
+            const uint64_t q_desc0 = desc_k_major(q_s);
+            const uint64_t k_desc0[2] = {desc_k_major(k_s), desc_k_major(k_s + STAGE)};
+            const uint64_t v_desc0[2] = {desc_mn_major(v_s, KV_ATOM), desc_mn_major(v_s + STAGE, KV_ATOM)};
             auto issue_s = [&](int i) {   // S of page i into S buffer i & 1
                 mbar_wait(&k_full[i & 1], (i >> 1) & 1, abort_flag, status);
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < PT_D / 16; ++ks)
-                    tc_mma(tmem + (i & 1) * SB_PAGE, q_desc[ks], (i & 1) ? k_desc[1][ks] : k_desc[0][ks], idesc_s, ks > 0 ? 1u : 0u);
+                    tc_mma(tmem + (i & 1) * SB_PAGE, q_desc0 + (ks >> 2) * (Q_ATOM >> 4) + 2 * (ks & 3),
+                           k_desc0[i & 1] + (ks >> 2) * (KV_ATOM >> 4) + 2 * (ks & 3), idesc_s, ks > 0 ? 1u : 0u);
                 tc_commit(&s_done[i & 1]);
             };
             issue_s(0);
@@ -203,7 +206,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 tc_fence_after();
 #pragma unroll
                 for (int ks = 0; ks < SB_PAGE / 16; ++ks)   // 16 keys per step: 32 bytes = 8 columns along P's rows
-                    tc_mma_ts(tmem + O_COL, tmem + b * SB_PAGE + 8 * ks, b ? v_desc[1][ks] : v_desc[0][ks], idesc_o,
+                    tc_mma_ts(tmem + O_COL, tmem + b * SB_PAGE + 8 * ks, v_desc0[b] + ks * (2048 >> 4), idesc_o,
                               (i > 0 || ks > 0) ? 1u : 0u);
                 tc_commit(&o_done[b]);
                 PT_STAMP(i, 2);
@@ -233,7 +236,11 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 while (clock64() - t_abort < (1ll << 22)) {}
             }
         }
+        tc_fence_before();
+        __syncthreads();   // the block's last meeting: the rows free tensor memory after it
+        return;
     } else {
+        asm volatile("setmaxnreg.inc.sync.aligned.u32 216;" ::: "memory");
         // ---- the rows.  The output accumulates in tensor memory across pages.  The probabilities of a page are
         // taken relative to a reference maximum m_ref that is raised only when the row's maximum exceeds it by
         // more than 8 (in the log2 domain): then the row's sum and its accumulator are rescaled once.  Until then
@@ -362,10 +369,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_c
                 }
             }
         }
+        tc_fence_before();
+        __syncthreads();
+        if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
     }
-    tc_fence_before();
-    __syncthreads();
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(256u) : "memory");
 }
 
 // ---- host side ----------------------------------------------------------------------------------
