@@ -68,28 +68,35 @@ def bench_product(ops, kernel: str, shape: str, rows: int, copies: int):
             "GB/s": round(nbytes / us / 1e3, 1)}
 
 
-def bench_attn_decode(ops, rows: int, context: int, heads: int, kv_heads: int, head_dim: int, layers: int):
+def bench_attn_decode(ops, rows: int, context: int, heads: int, kv_heads: int, head_dim: int, layers: int, long_context: int = 0):
+    """One new token per sequence over caches of ``context`` tokens; with ``long_context`` the first sequence holds
+    that many instead, and the step's context carries the hint that the lengths are very unequal when they are."""
     from ..cache import Cache, KVRequest
-    from ..engine.context import Runtime, StepContext
+    from ..engine.context import Runtime, StepContext, lengths_uneven
     dtype = torch.bfloat16
-    cache = Cache([KVRequest(kv_heads, head_dim)] * layers, n_slots=rows, max_tokens=rows * context, dtype=dtype,
-                  device="cuda", max_seq_tokens=context)
+    lengths = [max(long_context, 1) if long_context and i == 0 else context for i in range(rows)]
+    cache = Cache([KVRequest(kv_heads, head_dim)] * layers, n_slots=rows, max_tokens=sum(-(-n // 64) * 64 for n in lengths),
+                  dtype=dtype, device="cuda", max_seq_tokens=max(lengths))
     cache.groups[0].k.normal_()
     cache.groups[0].v.normal_()
     slots = [cache.alloc() for _ in range(rows)]
-    for s in slots:
-        cache.assume_length(s, context - 1)
+    for s, n in zip(slots, lengths):
+        cache.assume_length(s, n - 1)
     cache.flush()
     i32 = lambda v: torch.tensor(v, dtype=torch.int32, device="cuda")
     ctx = StepContext(runtime=Runtime(dtype, torch.device("cuda"), ops), cache=cache, n_seqs=rows, n_rows=rows, max_q_len=1,
-                      kv_bound=context, seq_slot=i32(slots), cu_q=i32(list(range(rows + 1))), row_seq=i32(list(range(rows))),
-                      lengths=cache.lengths, status=torch.zeros(1, dtype=torch.int32, device="cuda"))
+                      kv_bound=max(lengths), seq_slot=i32(slots), cu_q=i32(list(range(rows + 1))), row_seq=i32(list(range(rows))),
+                      lengths=cache.lengths, status=torch.zeros(1, dtype=torch.int32, device="cuda"),
+                      uneven=lengths_uneven(lengths))
     q = torch.randn(rows, heads * head_dim, device="cuda", dtype=dtype)
     calls = [lambda lc=lc: ops.attention(ctx, q, lc, heads, 1.0 / math.sqrt(head_dim), None) for lc in cache.layers]
     us = time_graph(calls)
-    nbytes = rows * context * kv_heads * head_dim * 2 * 2
-    return {"kernel": "attn_decode", "rows": rows, "context": context, "us": round(us, 2), "cache_bytes": nbytes,
-            "GB/s": round(nbytes / us / 1e3, 1)}
+    nbytes = sum(lengths) * kv_heads * head_dim * 2 * 2
+    out = {"kernel": "attn_decode", "rows": rows, "context": context, "us": round(us, 2), "cache_bytes": nbytes,
+           "GB/s": round(nbytes / us / 1e3, 1)}
+    if long_context:
+        out.update(long_context=long_context, uneven=ctx.uneven)
+    return out
 
 
 def bench_attn_prefill(ops, tokens: int, context: int, heads: int, kv_heads: int, head_dim: int, layers: int):
@@ -161,6 +168,7 @@ def main(argv=None) -> int:
     ap.add_argument("--rows", type=int, default=8)
     ap.add_argument("--copies", type=int, default=12, help="copies of the weights the graph walks through")
     ap.add_argument("--context", type=int, default=4096)
+    ap.add_argument("--long-context", type=int, default=0, help="attn_decode: the first sequence holds this many tokens instead")
     ap.add_argument("--tokens", type=int, default=2048, help="attn_prefill: new tokens of the sequence")
     ap.add_argument("--layers", type=int, default=8, help="attn_decode: layers of cache the graph walks through")
     ap.add_argument("--dependent-launch", action="store_true", help="launch with programmatic dependent launch")
@@ -173,7 +181,7 @@ def main(argv=None) -> int:
     elif args.kernel == "attn_prefill":
         out = bench_attn_prefill(ops, args.tokens, max(args.context, args.tokens), 32, 8, 128, args.layers)
     elif args.kernel == "attn_decode":
-        out = bench_attn_decode(ops, args.rows, args.context, 32, 8, 128, args.layers)
+        out = bench_attn_decode(ops, args.rows, args.context, 32, 8, 128, args.layers, args.long_context)
     else:
         out = bench_product(ops, args.kernel, args.shape, args.rows, args.copies)
     print(json.dumps(out))

@@ -511,7 +511,8 @@ class Ops:
         191 / 173; in the step at batch 64: 8.50 / 8.36 ms.  The balanced kernel pays ~6 us before its first page and its
         blocks end up to 10 us apart; blocks handed out one by one even that out by themselves.  With very unequal
         lengths (``ctx.uneven``: the longest sequence more than three times the mean) a block per pair would leave the
-        longest to one block, and the balanced kernel takes over where the pairs outnumber the blocks that fit."""
+        longest to one block, and the balanced kernel takes over where the pairs outnumber the blocks that fit: batch 64
+        with 63 sequences of 256 tokens and one of 16,384: 43 us against 162 (one of 4,096: 34 against 53)."""
         if kv.head_dim not in (64, 128) or n_heads % kv.n_kv_heads or n_heads // kv.n_kv_heads > 16:
             return None
         if not (ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs):
