@@ -115,8 +115,7 @@ class Ops:
         self._kernel_status = None
         self._status_override = None
         self.decode_balanced = os.environ.get("STARTER_B200_ATTN", "balanced") != "split"
-        self.force_decode_route = None   # "split" or "balanced" for tests; None = the rule in _decode_route
-        self._most_kv_heads = 1          # the most kv heads a decode step has brought so far (for uneven_matters)
+        self.force_decode_route = os.environ.get("STARTER_B200_ATTN_ROUTE") or None   # "split" or "balanced", for tests and tuning runs; None = the rule in _decode_route
         self.fuse_qk = os.environ.get("STARTER_B200_FUSE_QK", "1") != "0"
         # With the balanced kernel (more pairs than blocks fit at once) the preparation stays a kernel of its own: a block
         # walks several (sequence, kv head) pairs one after another and pays each pair's preparation on its own path.
@@ -510,28 +509,24 @@ class Ops:
         batch 64 at context 2,048: 95.8 / 87.9, at 4,096: 168.3 / 163.8; batch 128 at 2,048: 175 / 169; batch 256 at 1,024:
         191 / 173; in the step at batch 64: 8.50 / 8.36 ms.  The balanced kernel pays ~6 us before its first page and its
         blocks end up to 10 us apart; blocks handed out one by one even that out by themselves.  With very unequal
-        lengths (``ctx.uneven``: the longest sequence more than three times the mean) a block per pair would leave the
-        longest to one block, and the balanced kernel takes over where the pairs outnumber the blocks that fit: batch 64
-        with 63 sequences of 256 tokens and one of 16,384: 43 us against 162 (one of 4,096: 34 against 53)."""
+        lengths (``ctx.uneven``: the longest sequence more than three times the mean) the split kernel, whose blocks per
+        pair are a matter of shapes, leaves the longest sequence to a few blocks, and the balanced kernel takes over at
+        every batch size.  One sequence of 16,384 tokens among others of 256 (us, split / balanced): batch 8: 81 / 27,
+        batch 16: 83 / 34, batch 32: 153 / 41, batch 64: 162 / 43; one of 4,096: 18 / 20, 27 / 21, 45 / 28, 53 / 34."""
         if kv.head_dim not in (64, 128) or n_heads % kv.n_kv_heads or n_heads // kv.n_kv_heads > 16:
             return None
         if not (ctx.max_q_len == 1 and ctx.n_rows == ctx.n_seqs):
             return None
         if self.force_decode_route is not None:
             return self.force_decode_route
-        self._most_kv_heads = max(self._most_kv_heads, kv.n_kv_heads)
-        pairs = ctx.n_seqs * kv.n_kv_heads
-        if (self.decode_balanced and getattr(ctx, "uneven", False) and pairs > self.decode_resident(kv.head_dim)
-                and ctx.n_seqs <= 1024):
+        if self.decode_balanced and getattr(ctx, "uneven", False) and ctx.n_seqs <= 1024:
             return "balanced"
         return "split"
 
     def uneven_matters(self, n_seqs: int) -> bool:
         """Whether a decode step of this many sequences would run other kernels when its context says ``uneven``
         (so that a caller who keeps captured graphs need not keep two alike)."""
-        if self.force_decode_route is not None or not self.decode_balanced:
-            return False
-        return n_seqs <= 1024 and n_seqs * self._most_kv_heads > self.decode_resident(128)
+        return self.force_decode_route is None and self.decode_balanced and 2 <= n_seqs <= 1024
 
     def _split_decode(self, ctx, kv, n_heads) -> bool:
         return self._decode_route(ctx, kv, n_heads) == "split"
