@@ -95,3 +95,17 @@ def test_slots_come_back_when_the_caller_stops_listening(tiny_folders):
     gen.close()
     assert eng.session.cache.slots.n_held == 0
     eng.session.cache.check()
+
+
+def test_very_unequal_lengths_are_told_from_the_rest():
+    """The hint that lets the kernels choose: the longest sequence holds more than three times the mean number of
+    cache pages.  Lengths within a page of one another are equal, a single sequence is never unequal."""
+    from starter_b200.engine.context import lengths_uneven
+    assert not lengths_uneven([])
+    assert not lengths_uneven([100000])
+    assert not lengths_uneven([1, 63, 40, 7])                 # one page each
+    assert not lengths_uneven([4096] * 64)
+    assert not lengths_uneven([64, 2048, 700, 1300, 90, 1999])   # uniform in [64, 2048]: the longest is twice the mean
+    assert lengths_uneven([16384] + [256] * 63)
+    assert lengths_uneven([4096] + [256] * 7)
+    assert not lengths_uneven([4096, 256])                    # two sequences: the longest can be at most twice the mean
