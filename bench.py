@@ -148,6 +148,15 @@ def prefill_flops(raw, n_layers, lengths):
     return linear + attention + 2.0 * len(lengths) * raw["vocab_size"] * raw["hidden_size"]
 
 
+def prefill_point(points, name, raw, n_layers, lengths, ms, peaks):
+    """A further prefill measurement as flat numbers: tokens a second under ``name``, its time under
+    ``name_ms`` and its flops / time / the sustained bf16 peak under ``name_frac_of_sustained``."""
+    points[name] = round(sum(lengths) * 1000.0 / ms, 1)
+    points[name + "_ms"] = round(ms, 3)
+    points[name + "_frac_of_sustained"] = round(
+        prefill_flops(raw, n_layers, lengths) / (ms * 1e-3) / (peaks["bf16_tflops_sustained"] * 1e12), 4)
+
+
 def prompt_lengths(workload, seed=4):
     import torch
     B = workload["batch"]
@@ -322,15 +331,11 @@ def run_ours(args, raw, workload) -> int:
                "ms": round(prefill_ms, 3), "frac": round(prefill_frac, 4)}
     if long_prefill:
         ms = time_prefill(session, [long_prefill], repeats=2, torch=torch)
-        points[f"prefill_{long_prefill}"] = {"value": round(long_prefill * 1000.0 / ms, 1), "ms": round(ms, 3), "frac": round(
-            prefill_flops(raw, n_layers, [long_prefill]) / (ms * 1e-3) / (peaks["bf16_tflops_sustained"] * 1e12), 4),
-            "peak": "sustained"}
+        prefill_point(points, f"prefill_{long_prefill}", raw, n_layers, [long_prefill], ms, peaks)
     if not headline:  # the workload's own prompts, all in one step
         ms = time_prefill(session, lengths, repeats=2, torch=torch)
-        points["prefill_workload"] = {"value": round(sum(lengths) * 1000.0 / ms, 1), "tokens": sum(lengths),
-                                      "ms": round(ms, 3), "frac": round(
-            prefill_flops(raw, n_layers, lengths) / (ms * 1e-3) / (peaks["bf16_tflops_sustained"] * 1e12), 4),
-            "peak": "sustained"}
+        prefill_point(points, "prefill_workload", raw, n_layers, lengths, ms, peaks)
+        points["prefill_workload_tokens"] = sum(lengths)
 
     e2e = None
     if not args.skip_e2e:
@@ -535,10 +540,7 @@ def run_reference(args, raw, workload) -> int:
             prefill_ms = prefill_ms_of(PREFILL_TOKENS, 3)
             if headline and not args.skip_points:
                 ms = prefill_ms_of(LONG_PREFILL_TOKENS, 2)
-                points[f"prefill_{LONG_PREFILL_TOKENS}"] = {
-                    "value": round(LONG_PREFILL_TOKENS * 1000.0 / ms, 1), "ms": round(ms, 3), "frac": round(
-                        prefill_flops(raw, n_layers, [LONG_PREFILL_TOKENS]) / (ms * 1e-3) /
-                        (peaks["bf16_tflops_sustained"] * 1e12), 4), "peak": "sustained"}
+                prefill_point(points, f"prefill_{LONG_PREFILL_TOKENS}", raw, n_layers, [LONG_PREFILL_TOKENS], ms, peaks)
         except Exception as exc:  # noqa: BLE001
             return _unavailable(f"the reference's engine failed on this box: {exc!r}")
     finally:
