@@ -604,6 +604,10 @@ def main() -> int:
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         return run_reference(args, raw, workload)
+    import torch
+    if not torch.cuda.is_available():   # no fallback: the library's kernels are the thing measured
+        print("bench.py needs a CUDA device (sm_100a) and found none", file=sys.stderr)
+        return 1
     if args.check:
         return run_check(args, raw, workload)
     return run_ours(args, raw, workload)
